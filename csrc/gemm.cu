@@ -1,0 +1,310 @@
+// bf16 GEMM family for sm_100a: C[M,N] = alpha * A[M,K] * B[N,K]^T (+ C), fp32 accumulation in TMEM.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0     TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1     MMA issuer    (tcgen05.mma cta_group::1, M=128, N=BLOCK_N, K=16 per instruction)
+//   warps 2-5  epilogue      (tcgen05.ld 32x32b, convert, store; overlaps the next tile's main loop
+//                             through two TMEM accumulators)
+// Either operand may be K-major (rows of K contiguous) or MN-major (the M/N index contiguous), so
+// the three GEMMs of a linear layer (Y = X W^T, dX = dY W, dW = dY^T X) run without a transpose.
+// The fp32 output mode with accumulate writes weight gradients straight into a flat fp32 gradient
+// buffer (the cast and the micro-batch accumulation of a sharded-data-parallel step).
+#include "common.cuh"
+#include "yafsdp_b200.h"
+
+YF_TU_STATUS()
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+template <int BLOCK_N>
+struct GemmCfg {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+};
+
+struct GemmArgs {
+  void* C;
+  int M, N, K;
+  long long ldc;
+  float alpha;
+  int a_mn, b_mn, out_f32, accumulate;
+};
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         GemmArgs args) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                 // [STAGES]
+  uint64_t* empty = bars + STAGES;       // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty = tfull + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int M = args.M, N = args.N, K = args.K;
+  const int num_m = (M + BLOCK_M - 1) / BLOCK_M;
+  const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_k = (K + BLOCK_K - 1) / BLOCK_K;
+  const int num_tiles = num_m * num_n;
+  constexpr int GROUP_M = 16;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(GROUP_M, num_m - first_m);
+    const int r = t - g * per_group;
+    m0 = (first_m + r % gsize) * BLOCK_M;
+    n0 = (r / gsize) * BLOCK_N;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int m0, n0;
+        tile_coords(t, m0, n0);
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, 10)) { alive = false; break; }
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          const int k0 = kb * BLOCK_K;
+          if (!args.a_mn) {
+            tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * (BLOCK_K * 128), &tma_a, &full[s], m0 + j * 64, k0);
+          }
+          if (!args.b_mn) {
+            tma_load_2d(sb, &tma_b, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * (BLOCK_K * 128), &tma_b, &full[s], n0 + j * 64, k0);
+          }
+        }
+      }
+      if (!alive) {
+        // give copies already in flight a bounded time to land before the CTA may exit
+        const uint64_t t0 = yf_globaltimer();
+        while (yf_globaltimer() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BLOCK_M, BLOCK_N, args.a_mn, args.b_mn);
+      const uint32_t a_lbo = args.a_mn ? BLOCK_K * 128 : 0, b_lbo = args.b_mn ? BLOCK_K * 128 : 0;
+      const uint32_t a_kstep = args.a_mn ? UMMA_K * 128 : UMMA_K * 2, b_kstep = args.b_mn ? UMMA_K * 128 : UMMA_K * 2;
+      uint32_t it = 0;
+      bool alive = true;
+      int lt = 0;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++lt) {
+        const int acc = lt & 1;
+        const uint32_t acc_ph = (lt >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, 20)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, 21)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            tc_mma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
+        }
+        if (alive) tc_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
+    const int q = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+    bool alive = true;
+    int lt = 0;
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++lt) {
+      int m0, n0;
+      tile_coords(t, m0, n0);
+      const int acc = lt & 1;
+      const uint32_t acc_ph = (lt >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, 30)) { alive = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
+      const float alpha = args.alpha;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          const bool fullw = (col + 32 <= N);
+          if (args.out_f32) {
+            float* dst = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+            if (fullw) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o;
+                o.x = alpha * __uint_as_float(r[4 * v + 0]);
+                o.y = alpha * __uint_as_float(r[4 * v + 1]);
+                o.z = alpha * __uint_as_float(r[4 * v + 2]);
+                o.w = alpha * __uint_as_float(r[4 * v + 3]);
+                float4* p = reinterpret_cast<float4*>(dst) + v;
+                if (args.accumulate) {
+                  const float4 old = *p;
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *p = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) {
+                float o = alpha * __uint_as_float(r[j]);
+                if (args.accumulate) o += dst[j];
+                dst[j] = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col;
+            if (fullw) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = alpha * __uint_as_float(r[8 * v + j]);
+                uint4* p = reinterpret_cast<uint4*>(dst) + v;
+                if (args.accumulate) {
+                  const uint4 old = *p;
+                  float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
+                         a3 = unpack_bf16x2(old.w);
+                  f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y;
+                  f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *p = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) {
+                float o = alpha * __uint_as_float(r[j]);
+                if (args.accumulate) o += __bfloat162float(dst[j]);
+                dst[j] = __float2bfloat16_rn(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BLOCK_N>
+int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long lda, long long ldb, int sm_limit,
+                cudaStream_t stream) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(A, args.M, args.K, lda, 64, BLOCK_K, 2, 1)
+                                    : yf_tensor_map_2d(A, args.K, args.M, lda, BLOCK_K, BLOCK_M, 2, 1);
+  const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(B, args.N, args.K, ldb, 64, BLOCK_K, 2, 1)
+                                    : yf_tensor_map_2d(B, args.K, args.N, ldb, BLOCK_K, BLOCK_N, 2, 1);
+  if (!ma || !mb) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    attr_set = true;
+  }
+  const int num_tiles = ((args.M + BLOCK_M - 1) / BLOCK_M) * ((args.N + BLOCK_N - 1) / BLOCK_N);
+  int sms = yf_num_sms();
+  if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, args);
+  return -(int)cudaGetLastError();
+}
+
+}  // namespace
+
+// C[M,N] = alpha * A * B^T (+ C).  A is [M,K] with row pitch lda (a_mn = 0) or stored as [K,M] with row
+// pitch lda (a_mn = 1); B likewise as [N,K] (b_mn = 0) or [K,N] (b_mn = 1).  bf16 inputs; C is bf16 or
+// fp32 (out_f32) with row pitch ldc.  Pitches are in elements and must be multiples of 8 (16-byte TMA
+// strides); base pointers must be 16-byte aligned.  sm_limit > 0 caps the persistent grid (leaves SMs
+// to a concurrent communication kernel).
+extern "C" int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                            long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit,
+                            void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
+  GemmArgs args;
+  args.C = C;
+  args.M = M; args.N = N; args.K = K;
+  args.ldc = ldc;
+  args.alpha = alpha;
+  args.a_mn = a_mn ? 1 : 0;
+  args.b_mn = b_mn ? 1 : 0;
+  args.out_f32 = out_f32 ? 1 : 0;
+  args.accumulate = accumulate ? 1 : 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // 128x256 tiles unless N is small or the 256-wide tiling wastes more of the last column block
+  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
+  return use256 ? launch_gemm<256>(A, B, args, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, lda, ldb, sm_limit, s);
+}

@@ -1,0 +1,41 @@
+// C interface of the native sm_100a library (libyafsdp_b200.so).  Every function launches on the
+// given CUDA stream (a cudaStream_t passed as void*) and returns 0 on success, a negative value on
+// a rejected argument (-1), a tensor-map failure (-2) or a CUDA error (-cudaError_t).  Nothing here
+// synchronises the device except yf_status_read().  Python binds these symbols through ctypes.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int yf_version(void);
+int yf_sm_count(void);
+// First error recorded by any kernel since the last clearing read (0 = none); synchronous.
+int yf_status_read(int* code, int* site, int clear);
+
+// ---- tcgen05 GEMM family (gemm.cu)
+int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                 long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit, void* stream);
+
+// ---- memory-bound kernels (elementwise.cu)
+int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream);
+int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
+                   float* dw, int T, int D, void* stream);
+int yf_rope(void* qkv, const float* cos_sin, int T, int seq_len, long long row_stride, int col0, int n_heads,
+            int head_dim, int backward, void* stream);
+int yf_swiglu_fwd(const void* gu, void* h, long long T, int F, void* stream);
+int yf_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long T, int F, void* stream);
+int yf_cross_entropy(void* logits, const long long* labels, float* loss_rows, int T, int V, long long ldl,
+                     float grad_scale, int write_grad, void* stream);
+int yf_embedding_fwd(const void* table, const long long* ids, void* out, long long T, int D, int V, void* stream);
+int yf_embedding_bwd(const void* dout, const long long* ids, float* dtable, long long T, int D, int V, void* stream);
+int yf_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, const float* grad_scale_ptr, long long n,
+             float lr, float beta1, float beta2, float eps, float weight_decay, int step, void* stream);
+int yf_sumsq(const float* g, long long n, float* out, void* stream);
+int yf_clip_coef(const float* total_sq, float max_norm, float* coef, float* norm_out, void* stream);
+int yf_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+int yf_accum_bf16_to_f32(const void* src, float* dst, long long n, float scale, int accumulate, void* stream);
+int yf_add_bf16(const void* a, const void* b, void* y, long long n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,206 @@
+"""Thin tensor-level wrappers over the native sm_100a kernels (``csrc/*.cu``).
+
+Each function checks its arguments on the host, launches on the current CUDA stream and raises on a
+non-zero return code.  ``launch_count()`` counts every launch made through this module (the
+benchmark reports it).  Nothing here falls back to PyTorch: a missing library on a GPU machine is an
+error, and the autograd-level ops in :mod:`yafsdp_b200.ops.functional` choose between this module
+(CUDA tensors) and plain PyTorch math (CPU tensors).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, name: str) -> None:
+    global _launches
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+    _launches += 1
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status(clear: bool = True) -> tuple[int, int]:
+    """(code, site) of the first error any kernel recorded since the last clearing read.  Synchronises."""
+    code = ctypes.c_int(0)
+    site = ctypes.c_int(0)
+    rc = _native.lib().yf_status_read(ctypes.byref(code), ctypes.byref(site), int(clear))
+    if rc != 0:
+        raise RuntimeError(f"yf_status_read failed with code {rc}")
+    return code.value, site.value
+
+
+def check_status() -> None:
+    code, site = status()
+    if code != 0:
+        raise RuntimeError(f"a native kernel reported error {code} at site {site} (bounded wait ran out)")
+
+
+# --------------------------------------------------------------------------------------- GEMM
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn_major: bool = False,
+    b_mn_major: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    sm_limit: int = 0,
+) -> torch.Tensor:
+    """``out[M,N] = alpha * A @ B^T (+ out)`` with bf16 inputs and fp32 accumulation (tcgen05).
+
+    ``a`` is ``[M,K]`` (K-major) or, with ``a_mn_major``, the stored tensor is ``[K,M]``; ``b`` is
+    ``[N,K]`` or, with ``b_mn_major``, stored ``[K,N]``.  Rows must be contiguous (stride 1 in the last
+    dimension); the row pitch may exceed the row length.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn_major:
+        k, m = a.shape
+    else:
+        m, k = a.shape
+    if b_mn_major:
+        kb, n = b.shape
+    else:
+        n, kb = b.shape
+    assert k == kb, f"inner dimensions differ: {k} vs {kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    rc = _native.lib().yf_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), float(alpha),
+        int(sm_limit), _stream(),
+    )
+    _check(rc, "yf_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------------------- norms etc.
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+    t, d = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(t, device=x.device, dtype=torch.float32)
+    _check(_native.lib().yf_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), t, d, float(eps), _stream()),
+           "yf_rmsnorm_fwd")
+    return y, rstd
+
+
+def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, rstd: torch.Tensor, dw_f32: torch.Tensor,
+                dres: torch.Tensor | None = None) -> torch.Tensor:
+    """Returns dx (+ dres when given); accumulates the weight gradient into the fp32 tensor ``dw_f32``."""
+    t, d = x.shape
+    dx = torch.empty_like(x)
+    assert dw_f32.dtype == torch.float32 and dw_f32.numel() == d
+    _check(_native.lib().yf_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), _ptr(dres), dx.data_ptr(),
+                                        dw_f32.data_ptr(), t, d, _stream()), "yf_rmsnorm_bwd")
+    return dx
+
+
+def rope_(qkv: torch.Tensor, cos_sin: torch.Tensor, seq_len: int, col0: int, n_heads: int, head_dim: int,
+          backward: bool = False) -> torch.Tensor:
+    """Rotate ``n_heads`` heads of ``qkv[T, :]`` starting at column ``col0`` in place."""
+    t = qkv.shape[0]
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and cos_sin.dtype == torch.float32
+    _check(_native.lib().yf_rope(qkv.data_ptr(), cos_sin.data_ptr(), t, seq_len, qkv.stride(0), col0, n_heads, head_dim,
+                                 int(backward), _stream()), "yf_rope")
+    return qkv
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    t, f2 = gu.shape
+    h = torch.empty((t, f2 // 2), device=gu.device, dtype=gu.dtype)
+    _check(_native.lib().yf_swiglu_fwd(gu.data_ptr(), h.data_ptr(), t, f2 // 2, _stream()), "yf_swiglu_fwd")
+    return h
+
+
+def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
+    t, f2 = gu.shape
+    dgu = torch.empty_like(gu)
+    _check(_native.lib().yf_swiglu_bwd(gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), t, f2 // 2, _stream()), "yf_swiglu_bwd")
+    return dgu
+
+
+def cross_entropy_(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float, write_grad: bool = True) -> torch.Tensor:
+    """Per-row losses; ``logits`` is overwritten by ``(softmax - onehot) * grad_scale`` when ``write_grad``."""
+    t, v = logits.shape
+    assert labels.dtype == torch.int64 and logits.stride(1) == 1
+    loss_rows = torch.empty(t, device=logits.device, dtype=torch.float32)
+    _check(_native.lib().yf_cross_entropy(logits.data_ptr(), labels.data_ptr(), loss_rows.data_ptr(), t, v, logits.stride(0),
+                                          float(grad_scale), int(write_grad), _stream()), "yf_cross_entropy")
+    return loss_rows
+
+
+def embedding_fwd(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    v, d = table.shape
+    t = ids.numel()
+    out = torch.empty((t, d), device=table.device, dtype=table.dtype)
+    _check(_native.lib().yf_embedding_fwd(table.data_ptr(), ids.data_ptr(), out.data_ptr(), t, d, v, _stream()), "yf_embedding_fwd")
+    return out
+
+
+def embedding_bwd_(dout: torch.Tensor, ids: torch.Tensor, dtable_f32: torch.Tensor) -> None:
+    v, d = dtable_f32.shape
+    _check(_native.lib().yf_embedding_bwd(dout.data_ptr(), ids.data_ptr(), dtable_f32.data_ptr(), ids.numel(), d, v, _stream()),
+           "yf_embedding_bwd")
+
+
+def adamw_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, p_bf16: torch.Tensor | None,
+           grad_scale: torch.Tensor | None, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+           step: int) -> None:
+    n = p.numel()
+    assert p.dtype == g.dtype == m.dtype == v.dtype == torch.float32
+    _check(_native.lib().yf_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _ptr(p_bf16), _ptr(grad_scale), n,
+                                  float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step), _stream()),
+           "yf_adamw")
+
+
+def sumsq_(g: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[0] += sum(g*g)`` (fp32)."""
+    _check(_native.lib().yf_sumsq(g.data_ptr(), g.numel(), out.data_ptr(), _stream()), "yf_sumsq")
+
+
+def clip_coef_(total_sq: torch.Tensor, max_norm: float, coef: torch.Tensor, norm_out: torch.Tensor | None) -> None:
+    _check(_native.lib().yf_clip_coef(total_sq.data_ptr(), float(max_norm), coef.data_ptr(), _ptr(norm_out), _stream()), "yf_clip_coef")
+
+
+def cast_f32_to_bf16_(src: torch.Tensor, dst: torch.Tensor) -> None:
+    assert src.numel() == dst.numel()
+    _check(_native.lib().yf_cast_f32_to_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), _stream()), "yf_cast_f32_to_bf16")
+
+
+def accum_bf16_to_f32_(src: torch.Tensor, dst: torch.Tensor, scale: float = 1.0, accumulate: bool = False) -> None:
+    assert src.numel() == dst.numel()
+    _check(_native.lib().yf_accum_bf16_to_f32(src.data_ptr(), dst.data_ptr(), src.numel(), float(scale), int(accumulate), _stream()),
+           "yf_accum_bf16_to_f32")
+
+
+def add_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    out = torch.empty_like(a) if out is None else out
+    _check(_native.lib().yf_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "yf_add_bf16")
+    return out

@@ -1,0 +1,362 @@
+// Causal flash-attention backward for head_dim 128 on sm_100a (MHA and GQA).
+//
+// One CTA per (128-key tile, KV head, sequence); it walks the query tiles (and, for GQA, the query
+// heads of the group) that attend to those keys.  Per step five tcgen05 GEMMs:
+//   S  = Q K^T          dP = dO V^T                    (fp32 in TMEM, one query row per TMEM lane)
+//   P  = exp(S*scale - lse),  dS = P * (dP - D) * scale   (softmax warps; bf16 into swizzled smem)
+//   dV += P^T dO        dK += dS^T Q                   (accumulated in TMEM over the whole walk)
+//   dQ_part = dS K      -> fp32 vector reductions into a global dQ accumulator
+// The P / dS tiles are stored once as [query][key] with the 128-byte swizzle and are read both as a
+// K-major operand (dQ) and as an MN-major operand (dV, dK): the two canonical layouts coincide.
+// D = rowsum(dO * O) comes from a small pre-pass; dQ is converted to bf16 by a post-pass.
+#include "common.cuh"
+#include "yafsdp_b200.h"
+
+YF_TU_STATUS()
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int ATOM = 16384;
+constexpr int TILE = 2 * ATOM;
+constexpr int BWD_THREADS = 192;
+constexpr int BWD_SMEM = 1024 + 6 * TILE + 256;
+
+struct BwdArgs {
+  const float* lse;    // [B, Hq, S]
+  const float* delta;  // [B, Hq, S]
+  float* dq_accum;     // [B*S, Hq*128] fp32, zeroed by the caller
+  __nv_bfloat16* dk;   // rows dkv_stride apart, head hk at columns hk*128
+  __nv_bfloat16* dv;
+  long long dkv_stride;
+  int S, B, Hq, Hkv;
+  float scale, scale_log2;
+  int causal;
+};
+
+YF_DEVINL void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do, BwdArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;
+  uint8_t* sdO = sQ + TILE;
+  uint8_t* sP = sdO + TILE;
+  uint8_t* sdS = sP + TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + TILE);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* pds_ready = bars + 4;
+  uint64_t* dq_full = bars + 5;
+  uint64_t* dq_read = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int jt = blockIdx.x;  // key tile
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int group = args.Hq / args.Hkv;
+  const int kv0 = jt * BKV;
+  const int nq_tiles = (args.S + BQ - 1) / BQ;
+  const int i_start = args.causal ? jt : 0;
+  const int per_head = nq_tiles - i_start;
+  const int n_it = per_head * group;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tma_q);
+    tma_prefetch_desc(&tma_k);
+    tma_prefetch_desc(&tma_v);
+    tma_prefetch_desc(&tma_do);
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 128);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE);
+      tma_load_3d(sK, &tma_k, kv_full, hk * HD, kv0, b);
+      tma_load_3d(sK + ATOM, &tma_k, kv_full, hk * HD + 64, kv0, b);
+      tma_load_3d(sV, &tma_v, kv_full, hk * HD, kv0, b);
+      tma_load_3d(sV + ATOM, &tma_v, kv_full, hk * HD + 64, kv0, b);
+      for (int it = 0; it < n_it; ++it) {
+        const int h = hk * group + it / per_head;
+        const int q0 = (i_start + it % per_head) * BQ;
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, 200)) break;
+        mbar_expect_tx(qdo_full, 2 * TILE);
+        tma_load_3d(sQ, &tma_q, qdo_full, h * HD, q0, b);
+        tma_load_3d(sQ + ATOM, &tma_q, qdo_full, h * HD + 64, q0, b);
+        tma_load_3d(sdO, &tma_do, qdo_full, h * HD, q0, b);
+        tma_load_3d(sdO + ATOM, &tma_do, qdo_full, h * HD + 64, q0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_kk = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t id_mm = umma_idesc_bf16(128, 128, 1, 1);
+      const uint32_t id_km = umma_idesc_bf16(128, 128, 0, 1);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      bool alive = mbar_wait(kv_full, 0, 210);
+      for (int it = 0; it < n_it && alive; ++it) {
+        if (!mbar_wait(qdo_full, it & 1, 211)) { alive = false; break; }
+        if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, 212)) { alive = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // S = Q K^T
+          const uint32_t off = (k >> 2) * ATOM + (k & 3) * 32;
+          tc_mma_bf16(tS, umma_smem_desc_sw128(aQ + off, 0, 1024), umma_smem_desc_sw128(aK + off, 0, 1024), id_kk, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // dP = dO V^T
+          const uint32_t off = (k >> 2) * ATOM + (k & 3) * 32;
+          tc_mma_bf16(tdP, umma_smem_desc_sw128(adO + off, 0, 1024), umma_smem_desc_sw128(aV + off, 0, 1024), id_kk, k != 0);
+        }
+        tc_commit(sdp_full);
+        if (!mbar_wait(pds_ready, it & 1, 213)) { alive = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV += P^T dO   (A = P read MN-major, B = dO MN-major; K = query rows)
+          tc_mma_bf16(tdV, umma_smem_desc_sw128(aP + k * 2048, ATOM, 1024), umma_smem_desc_sw128(adO + k * 2048, ATOM, 1024),
+                      id_mm, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK += dS^T Q
+          tc_mma_bf16(tdK, umma_smem_desc_sw128(adS + k * 2048, ATOM, 1024), umma_smem_desc_sw128(aQ + k * 2048, ATOM, 1024),
+                      id_mm, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ_part = dS K   (A = dS K-major over keys, B = K tile MN-major)
+          tc_mma_bf16(tS, umma_smem_desc_sw128(adS + (k >> 2) * ATOM + (k & 3) * 32, 0, 1024),
+                      umma_smem_desc_sw128(aK + k * 2048, ATOM, 1024), id_km, k != 0);
+        tc_commit(dq_full);
+        tc_commit(qdo_empty);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const float sl2 = args.scale_log2;
+    bool alive = true;
+    for (int it = 0; it < n_it && alive; ++it) {
+      const int h = hk * group + it / per_head;
+      const int q0 = (i_start + it % per_head) * BQ;
+      const int qrow = q0 + row;
+      const bool row_ok = qrow < args.S;
+      const long long stat_idx = ((long long)b * args.Hq + h) * args.S + qrow;
+      const float lse2 = row_ok ? args.lse[stat_idx] * 1.4426950408889634f : 0.f;
+      const float delta = row_ok ? args.delta[stat_idx] : 0.f;
+      // keys this query row may see: col <= limit
+      const int limit = row_ok ? (args.causal ? min(qrow, args.S - 1) : args.S - 1) : -1;
+      if (!mbar_wait(sdp_full, it & 1, 220)) { alive = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_off + c * 32, rs);
+        tmem_ld32(tdP + lane_off + c * 32, rp);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) {
+          float p0 = exp2f(fmaf(__uint_as_float(rs[t]), sl2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(rs[t + 1]), sl2, -lse2));
+          if (kv0 + c * 32 + t > limit) p0 = 0.f;
+          if (kv0 + c * 32 + t + 1 > limit) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rp[t]) - delta) * args.scale;
+          const float d1 = p1 * (__uint_as_float(rp[t + 1]) - delta) * args.scale;
+          pk[t >> 1] = pack_bf16x2(p0, p1);
+          dk[t >> 1] = pack_bf16x2(d0, d1);
+        }
+        const int tile_off = (c >> 1) * ATOM + row * 128;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int chunk = (((c & 1) * 4 + t) ^ (row & 7)) << 4;
+          *reinterpret_cast<uint4*>(sP + tile_off + chunk) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+          *reinterpret_cast<uint4*>(sdS + tile_off + chunk) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_ready);
+      if (!mbar_wait(dq_full, it & 1, 221)) { alive = false; break; }
+      tc_fence_after();
+      float* dq_row = args.dq_accum + ((long long)b * args.S + qrow) * ((long long)args.Hq * HD) + h * HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int t = 0; t < 32; t += 4)
+            red_add_v4(dq_row + c * 32 + t, __uint_as_float(r[t]), __uint_as_float(r[t + 1]), __uint_as_float(r[t + 2]),
+                       __uint_as_float(r[t + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_read);
+    }
+    // dK, dV: TMEM lane == key row.  The last dq_full wait covers every MMA issued before it.
+    if (alive) {  // every lane issues the (warp-collective) TMEM loads; only the stores are predicated
+      const bool key_ok = kv0 + row < args.S;
+      const long long off = ((long long)b * args.S + kv0 + row) * args.dkv_stride + hk * HD;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? args.dv : args.dk) + off;
+        const uint32_t tsrc = (which == 0 ? tdV : tdK) + lane_off;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tsrc + c * 32, r);
+          tmem_ld_wait();
+          if (key_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              w.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              w.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              w.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              reinterpret_cast<uint4*>(dst + c * 32)[v] = w;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b,h,s] = sum_d dO * O ; one warp per (token, head)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int S, int Hq, long long o_stride, long long do_stride) {
+  const long long total = (long long)B * S * Hq;
+  const int lane = threadIdx.x & 31;
+  for (long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; w < total;
+       w += ((long long)gridDim.x * blockDim.x) >> 5) {
+    const int h = (int)(w % Hq);
+    const long long t = w / Hq;
+    const uint2 a = *reinterpret_cast<const uint2*>(o + t * o_stride + h * HD + lane * 4);
+    const uint2 g = *reinterpret_cast<const uint2*>(d_o + t * do_stride + h * HD + lane * 4);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
+    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+    s = warp_sum(s);
+    if (lane == 0) {
+      const long long bb = t / S, ss = t % S;
+      delta[(bb * Hq + h) * S + ss] = s;
+    }
+  }
+}
+
+// dq (bf16, strided rows) = dq_accum (fp32, dense rows of `width`)
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long T, int width,
+                                       long long dq_stride) {
+  const int vpr = width / 8;
+  const long long total = T * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpr;
+    const int v = (int)(i % vpr);
+    const float4 a = reinterpret_cast<const float4*>(acc + t * width)[2 * v];
+    const float4 c = reinterpret_cast<const float4*>(acc + t * width)[2 * v + 1];
+    uint4 w;
+    w.x = pack_bf16x2(a.x, a.y);
+    w.y = pack_bf16x2(a.z, a.w);
+    w.z = pack_bf16x2(c.x, c.y);
+    w.w = pack_bf16x2(c.z, c.w);
+    *reinterpret_cast<uint4*>(dq + t * dq_stride + v * 8) = w;
+  }
+}
+
+}  // namespace
+
+// Backward of yf_attn_fwd.  q/k/v/out/dout as in the forward (dout rows do_stride apart, out rows
+// o_stride apart); lse from the forward.  Scratch supplied by the caller: delta [B,Hq,S] fp32 and
+// dq_accum [B*S, Hq*128] fp32 (zeroed here).  Results: dq (rows dq_stride apart), dk/dv (rows
+// dkv_stride apart), all bf16; they may be column blocks of one fused d(QKV) buffer.
+extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                           float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                           long long q_stride, long long kv_stride, long long o_stride, long long do_stride,
+                           long long dq_stride, long long dkv_stride, float scale, int causal, void* stream) {
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv)) return -1;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dq_stride % 8) || (dkv_stride % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
+       reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dq_accum)) & 15)
+    return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const CUtensorMap* mq = yf_tensor_map_3d(q, (uint64_t)Hq * HD, S, B, q_stride, (uint64_t)S * q_stride, 64, BQ, 1, 2, 1);
+  const CUtensorMap* mk = yf_tensor_map_3d(k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
+  const CUtensorMap* mv = yf_tensor_map_3d(v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
+  const CUtensorMap* md = yf_tensor_map_3d(dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1);
+  if (!mq || !mk || !mv || !md) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    attr_set = true;
+  }
+  const long long T = (long long)B * S;
+  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);
+  if (e != cudaSuccess) return -(int)e;
+  {
+    const long long warps = T * Hq;
+    long long blocks = (warps * 32 + 255) / 256;
+    const long long cap = (long long)yf_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_delta_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                  reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq, o_stride, do_stride);
+  }
+  BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.dq_accum = dq_accum;
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.dkv_stride = dkv_stride;
+  a.S = S; a.B = B; a.Hq = Hq; a.Hkv = Hkv;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal ? 1 : 0;
+  dim3 grid((S + BKV - 1) / BKV, Hkv, B);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(*mq, *mk, *mv, *md, a);
+  {
+    const long long items = T * (Hq * HD / 8);
+    long long blocks = (items + 255) / 256;
+    const long long cap = (long long)yf_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_dq_convert_kernel<<<(int)blocks, 256, 0, st>>>(dq_accum, reinterpret_cast<__nv_bfloat16*>(dq), T, Hq * HD, dq_stride);
+  }
+  return -(int)cudaGetLastError();
+}

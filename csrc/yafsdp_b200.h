@@ -36,6 +36,14 @@ int yf_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
 int yf_accum_bf16_to_f32(const void* src, float* dst, long long n, float scale, int accumulate, void* stream);
 int yf_add_bf16(const void* a, const void* b, void* y, long long n, void* stream);
 
+// ---- flash attention, head_dim 128 (attn_fwd.cu, attn_bwd.cu)
+int yf_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq, int Hkv,
+                long long q_stride, long long kv_stride, long long out_stride, float scale, int causal, void* stream);
+int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                long long q_stride, long long kv_stride, long long o_stride, long long do_stride, long long dq_stride,
+                long long dkv_stride, float scale, int causal, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

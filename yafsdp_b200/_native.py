@@ -151,8 +151,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_cast_f32_to_bf16": [_P, _P, _L, _P],
         "yf_accum_bf16_to_f32": [_P, _P, _L, _F, _I, _P],
         "yf_add_bf16": [_P, _P, _P, _L, _P],
-        "yf_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
-        "yf_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _F, _I, _P],
+        "yf_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _F, _I, _P],
+        "yf_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_allgather_pull": [_P, _P, _L, _I, _I, _I, _P],
         "yf_reduce_scatter_pull": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P],
         "yf_signal_barrier": [_P, _P, _I, _I, _L, _L, _P],

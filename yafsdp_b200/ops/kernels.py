@@ -204,3 +204,37 @@ def add_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) 
     out = torch.empty_like(a) if out is None else out
     _check(_native.lib().yf_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "yf_add_bf16")
     return out
+
+
+# --------------------------------------------------------------------------------------- attention
+def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq: int, n_heads: int, n_kv_heads: int,
+             scale: float, causal: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """Flash attention forward, head_dim 128.  ``q``: ``[B*S, Hq*128]`` view, ``k``/``v``: ``[B*S, Hkv*128]``
+    views (column blocks of the fused QKV projection output are fine).  Returns ``out [B*S, Hq*128]`` and
+    ``lse [B, Hq, S]``."""
+    t = batch * seq
+    assert q.shape == (t, n_heads * 128) and k.shape == (t, n_kv_heads * 128) and v.shape == k.shape
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and k.stride(0) == v.stride(0)
+    out = torch.empty((t, n_heads * 128), device=q.device, dtype=torch.bfloat16)
+    lse = torch.empty((batch, n_heads, seq), device=q.device, dtype=torch.float32)
+    _check(_native.lib().yf_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), batch, seq,
+                                     n_heads, n_kv_heads, q.stride(0), k.stride(0), out.stride(0), float(scale), int(causal),
+                                     _stream()), "yf_attn_fwd")
+    return out, lse
+
+
+def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
+             dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, batch: int, seq: int, n_heads: int, n_kv_heads: int,
+             scale: float, causal: bool = True) -> None:
+    """Flash attention backward into the given ``dq``/``dk``/``dv`` views (bf16, unit column stride)."""
+    t = batch * seq
+    assert dout.stride(1) == 1 and out.stride(1) == 1 and dq.stride(1) == 1 and dk.stride(1) == 1 and dv.stride(1) == 1
+    assert dk.stride(0) == dv.stride(0)
+    delta = torch.empty((batch, n_heads, seq), device=q.device, dtype=torch.float32)
+    dq_acc = torch.empty((t, n_heads * 128), device=q.device, dtype=torch.float32)
+    global _launches
+    _check(_native.lib().yf_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                                     delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), batch, seq,
+                                     n_heads, n_kv_heads, q.stride(0), k.stride(0), out.stride(0), dout.stride(0), dq.stride(0),
+                                     dk.stride(0), float(scale), int(causal), _stream()), "yf_attn_bwd")
+    _launches += 2  # delta pre-pass and dq conversion post-pass

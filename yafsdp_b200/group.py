@@ -1,0 +1,775 @@
+"""Parameter groups: flat ragged shards, rotating gather / reduce buffers, unshard / reshard.
+
+One ``ParamGroup`` holds every parameter that one ``fully_shard`` call manages:
+
+* a persistent flat master shard (original dtype, e.g. fp32) and a flat sharded gradient, both of
+  ``layout.shard_numel`` elements; every ``RaggedShardDTensor`` parameter / gradient is a view of them;
+* a flat all-gather input in the compute dtype (bf16 under mixed precision), refreshed from the master
+  once per optimizer step (or written directly by the fused AdamW kernel);
+* views into a *shared, rotating* gather buffer (the unsharded parameters) and a shared reduce buffer
+  (the unsharded fp32 gradients).  Buffers have an owner and a release event instead of going through
+  the caching allocator, so a layer's gather can be enqueued on the communication stream as soon as the
+  previous owner released the buffer.
+
+Blackwell-specific design on top of the reference's scheme (``ya_fsdp/_param_group.py:32-992``,
+``ya_fsdp/_param.py:44-372``):
+
+* *gradient sinks*: every unsharded parameter exposes ``_yf_grad_sink``; weight-gradient kernels (the
+  tcgen05 GEMM with an fp32 accumulating epilogue, RMSNorm / embedding backward) write straight into
+  the fp32 reduce buffer, so the bf16 gradient tensor, its cast and the copy into the flat buffer
+  disappear.  Plain ``autograd`` gradients (``param.grad``) still work and are copied in post-backward.
+* *single-rank aliasing*: with one rank the gather input IS the unsharded parameter storage and the
+  sharded gradient IS the reduce buffer, so there is no gather copy and no reduce copy at all.
+* the reduce-scatter fuses the averaging and the accumulation into the sharded gradient.
+"""
+
+from __future__ import annotations
+
+import contextlib
+from typing import Any, Callable, Iterator, NamedTuple
+
+import torch
+import torch.nn as nn
+from torch.profiler import record_function
+
+from .api import MixedPrecisionPolicy
+from .comm.backends import CommBackend, TorchBackend, gradient_divide_factors
+from .common import ShardMeshInfo, TrainingState, is_backward_running, logger
+from .layout import FlatLayout, ParamPlacement
+from .tensor import RaggedShard, RaggedShardDTensor, RaggedSpec, _contiguous_stride
+
+__all__ = ["ParamGroup", "BufferContext", "CommContext", "GradSink", "ShardedParam"]
+
+
+# ----------------------------------------------------------------------------------------- streams
+class _DeviceStreams:
+    """Stream / event helper that degrades to no-ops on CPU."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.is_cuda = device.type == "cuda"
+
+    def current(self) -> Any:
+        return torch.cuda.current_stream(self.device) if self.is_cuda else None
+
+    def new_stream(self, priority: int = 0) -> Any:
+        return torch.cuda.Stream(self.device, priority=priority) if self.is_cuda else None
+
+    def record(self, stream: Any = None) -> Any:
+        if not self.is_cuda:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(stream if stream is not None else self.current())
+        return ev
+
+    def wait_event(self, stream: Any, event: Any) -> None:
+        if self.is_cuda and event is not None:
+            (stream if stream is not None else self.current()).wait_event(event)
+
+    def wait_stream(self, stream: Any, other: Any) -> None:
+        if self.is_cuda and stream is not None and other is not None:
+            stream.wait_stream(other)
+
+    @contextlib.contextmanager
+    def use(self, stream: Any) -> Iterator[None]:
+        if self.is_cuda and stream is not None:
+            with torch.cuda.stream(stream):
+                yield
+        else:
+            yield
+
+
+class BufferContext:
+    """One shared rotating buffer (bytes) with an owner and a release event."""
+
+    def __init__(self, kind: str, index: int):
+        self.kind = kind  # "data" | "grad"
+        self.index = index
+        self.nbytes = 0
+        self.tensor: torch.Tensor | None = None
+        self.owner: "ParamGroup | None" = None
+        self.release_event: Any = None
+        self.users: list["ParamGroup"] = []
+
+    def lazy_init(self, nbytes: int, device: torch.device, backend: CommBackend) -> None:
+        if self.tensor is not None and self.nbytes >= nbytes:
+            return
+        self.nbytes = nbytes
+        self.tensor = backend.alloc(nbytes, torch.uint8, device, "gather_output" if self.kind == "data" else "reduce_input")
+
+    def view(self, dtype: torch.dtype, numel: int) -> torch.Tensor:
+        assert self.tensor is not None
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        return self.tensor[:nbytes].view(dtype)
+
+    def __repr__(self) -> str:
+        return f"BufferContext({self.kind}#{self.index}, {self.nbytes} B)"
+
+
+class CommContext:
+    """Streams shared by all groups of one root: one high-priority side stream carries both the
+    all-gathers and the reduce-scatters (``ya_fsdp/_param_group.py:74-101``)."""
+
+    def __init__(self) -> None:
+        self.streams: _DeviceStreams | None = None
+        self.all_gather_stream: Any = None
+        self.reduce_scatter_stream: Any = None
+        self.post_forward_order: list["ParamGroup"] = []
+        self.backend: CommBackend = TorchBackend()
+
+    def lazy_init(self, device: torch.device, backend: CommBackend | None = None) -> None:
+        self.streams = _DeviceStreams(device)
+        self.all_gather_stream = self.streams.new_stream(priority=-1)
+        self.reduce_scatter_stream = self.all_gather_stream
+        if backend is not None:
+            self.backend = backend
+
+    def get_all_gather_stream(self, async_op: bool, training_state: TrainingState) -> Any:
+        assert self.streams is not None
+        if not async_op and training_state in (TrainingState.FORWARD, TrainingState.PRE_BACKWARD):
+            return self.all_gather_stream
+        return self.streams.current()
+
+
+class GradSink:
+    """Destination of one parameter's weight gradient inside the flat fp32 reduce buffer.
+
+    ``begin()`` returns ``(fp32 view with the parameter's shape, accumulate)``: the first write of a
+    backward pass overwrites (the buffer holds another layer's stale data), later writes accumulate.
+    Kernels that can only add (atomics) call ``begin(zero=True)``.
+    """
+
+    __slots__ = ("group", "index", "view")
+
+    def __init__(self, group: "ParamGroup", index: int, view: torch.Tensor):
+        self.group = group
+        self.index = index
+        self.view = view
+
+    def begin(self, zero: bool = False) -> tuple[torch.Tensor, bool]:
+        g = self.group
+        g._acquire_grad_buffer()
+        accumulate = g._sink_written[self.index]
+        if not accumulate and g._alias_grad:
+            # single rank: the sink is the persistent sharded gradient itself, which may already hold
+            # the sum of earlier micro-batches
+            sp = g.params[self.index].sharded_param
+            accumulate = sp is not None and sp.grad is not None
+        g._sink_written[self.index] = True
+        if zero and not accumulate:
+            self.view.zero_()
+            accumulate = True
+        return self.view, accumulate
+
+
+class ParamModuleInfo(NamedTuple):
+    module: nn.Module
+    param_name: str
+    shared_modules: list[nn.Module]
+    shared_param_names: list[str]
+
+
+class ShardedParam:
+    """Sharded and unsharded incarnations of one parameter."""
+
+    def __init__(self, info: ParamModuleInfo, param: nn.Parameter, index: int):
+        self.info = info
+        self.index = index
+        self.orig_shape = param.shape
+        self.orig_dtype = param.dtype
+        self.numel = param.numel()
+        self.requires_grad = param.requires_grad
+        self.placement: ParamPlacement | None = None
+        self.sharded_param: nn.Parameter | None = None
+        self.sharded_grad: RaggedShardDTensor | None = None
+        self.unsharded_param: nn.Parameter | None = None
+        self.rs_view: torch.Tensor | None = None
+        self.sink: GradSink | None = None
+        self.is_unsharded = False
+        self.fqn: str | None = None
+
+    def _set(self, p: nn.Parameter) -> None:
+        # write module._parameters directly: nn.Module.__setattr__ is slow and these swaps are on the hot path
+        self.info.module._parameters[self.info.param_name] = p
+        for m, n in zip(self.info.shared_modules, self.info.shared_param_names):
+            m._parameters[n] = p
+
+    def to_sharded(self) -> None:
+        assert self.sharded_param is not None
+        self._set(self.sharded_param)
+        self.is_unsharded = False
+
+    def to_unsharded(self) -> None:
+        assert self.unsharded_param is not None
+        self._set(self.unsharded_param)
+        self.is_unsharded = True
+
+
+def _get_param_module_infos(params: list[nn.Parameter], modules: tuple[nn.Module, ...]) -> list[ParamModuleInfo]:
+    """Find the owning (module, name) of every parameter, plus other attributes sharing it (tied weights)."""
+    params_set = set(params)
+    found: dict[nn.Parameter, ParamModuleInfo] = {}
+    visited: set[nn.Module] = set()
+    for root in modules:
+        for _, sub in root.named_modules(remove_duplicate=False):
+            if sub in visited:
+                continue
+            visited.add(sub)
+            for name, p in sub.named_parameters(recurse=False):
+                if p in params_set:
+                    if p not in found:
+                        found[p] = ParamModuleInfo(sub, name, [], [])
+                    else:
+                        found[p].shared_modules.append(sub)
+                        found[p].shared_param_names.append(name)
+    if len(found) != len(params):
+        raise AssertionError(f"some parameters are not reachable from the wrapped modules ({len(found)} of {len(params)})")
+    return [found[p] for p in params]
+
+
+class ParamGroup:
+    """All parameters of one ``fully_shard`` call, communicated as one flat tensor."""
+
+    def __init__(
+        self,
+        params: list[nn.Parameter],
+        modules: tuple[nn.Module, ...],
+        mesh_info: ShardMeshInfo,
+        reshard_after_forward: bool,
+        device: torch.device,
+        mp_policy: MixedPrecisionPolicy,
+        shard_alignment: int = 8,
+    ):
+        self.modules = modules
+        self.mesh_info = mesh_info
+        self.device = device
+        self.mp_policy = mp_policy
+        self.world_size = mesh_info.shard_mesh_size
+        self.rank = mesh_info.shard_mesh_rank
+        self.process_group = mesh_info.shard_process_group
+        self._training_state = TrainingState.IDLE
+        self._module_fqn: str | None = None
+
+        infos = _get_param_module_infos(params, modules)
+        self.params = [ShardedParam(info, p, i) for i, (info, p) in enumerate(zip(infos, params))]
+        self._init_mp_dtypes(params)
+
+        # ---- flat layout and persistent shards
+        self.layout = FlatLayout([p.numel() for p in params], self.world_size, shard_alignment)
+        self._master = torch.zeros(self.layout.shard_numel, dtype=self.orig_dtype, device=device)
+        self._sharded_grad_flat: torch.Tensor | None = None
+        mesh = mesh_info.mesh
+        with torch.no_grad():
+            for sp, p in zip(self.params, params):
+                pl = self.layout.placement(sp.index, self.rank)
+                sp.placement = pl
+                local = self._master[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                if pl.local_numel and p.device.type != "meta":
+                    src = p.detach().reshape(-1)[pl.global_offset : pl.global_offset + pl.local_numel]
+                    local.copy_(src)
+                spec = RaggedSpec(
+                    mesh, (RaggedShard(pl.local_numel, pl.global_offset, pl.shard_numels),), torch.Size(sp.orig_shape),
+                    _contiguous_stride(sp.orig_shape), self.orig_dtype,
+                )
+                sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
+                for attr in ("_yf_init_fn",):
+                    if hasattr(p, attr):
+                        setattr(sp.sharded_param, attr, getattr(p, attr))
+                sp.to_sharded()
+        del params
+
+        # ---- runtime configuration
+        self.reshard_after_forward = reshard_after_forward
+        self.reshard_after_backward = True
+        self.reduce_grads = True
+        self.unshard_in_backward = True
+        self.unshard_async_op = False
+        self.gradient_divide_factor: float | None = None
+        self.force_sum_reduction_for_comms = False
+
+        # ---- set at lazy init
+        self.comm_ctx: CommContext | None = None
+        self.data_ctx: BufferContext | None = None
+        self.grad_ctx: BufferContext | None = None
+        self._lazy_inited = False
+        self._ag_input: torch.Tensor | None = None
+        self._ag_input_version = -1
+        self._ag_input_fresh = False
+        self._alias_data = False
+        self._alias_grad = False
+        self._ag_event: Any = None
+        self._unshard_pending = False
+        self._is_unsharded = False
+        self._post_reduce_event: Any = None
+        self._sink_written: list[bool] = [False] * len(self.params)
+        self._holds_grad_buffer = False
+        self._post_forward_indices: list[int] = []
+        self._partial_reduce_pending = False
+        self.modules_to_backward_prefetch: list[Any] = []
+        self.modules_to_forward_prefetch: list[Any] = []
+
+    # ------------------------------------------------------------------ dtypes
+    def _init_mp_dtypes(self, params: list[nn.Parameter]) -> None:
+        orig = {p.dtype for p in params}
+        if len(orig) != 1:
+            raise AssertionError(f"fully_shard expects uniform original parameter dtype per group, got {orig}")
+        self.orig_dtype = next(iter(orig))
+        pd, rd = self.mp_policy.param_dtype, self.mp_policy.reduce_dtype
+        if rd == pd:
+            rd = None
+        if pd == self.orig_dtype:
+            pd = None
+        self.param_dtype = pd
+        self.reduce_dtype = rd
+        self.all_gather_dtype = pd or self.orig_dtype
+        self.reduce_scatter_dtype = rd or pd or self.orig_dtype
+
+    # ------------------------------------------------------------------ sizes
+    @property
+    def padded_unsharded_numel(self) -> int:
+        return self.layout.padded_numel
+
+    def data_buffer_nbytes(self) -> int:
+        return self.layout.padded_numel * torch.empty((), dtype=self.all_gather_dtype).element_size()
+
+    def grad_buffer_nbytes(self) -> int:
+        return self.layout.padded_numel * torch.empty((), dtype=self.reduce_scatter_dtype).element_size()
+
+    @property
+    def sharded_grad_flat(self) -> torch.Tensor:
+        if self._sharded_grad_flat is None:
+            self._sharded_grad_flat = torch.zeros(self.layout.shard_numel, dtype=self.orig_dtype, device=self.device)
+            self._bind_sharded_grads()
+        return self._sharded_grad_flat
+
+    def _bind_sharded_grads(self) -> None:
+        assert self._sharded_grad_flat is not None
+        for sp in self.params:
+            pl = sp.placement
+            assert pl is not None and sp.sharded_param is not None
+            local = self._sharded_grad_flat[pl.shard_offset : pl.shard_offset + pl.local_numel]
+            sp.sharded_grad = RaggedShardDTensor(local, sp.sharded_param._spec.with_dtype(local.dtype))
+
+    @property
+    def master_flat(self) -> torch.Tensor:
+        return self._master
+
+    @property
+    def gather_input(self) -> torch.Tensor | None:
+        return self._ag_input
+
+    # ------------------------------------------------------------------ lazy init (root calls it once)
+    def lazy_init(self, comm_ctx: CommContext, data_ctx: BufferContext, grad_ctx: BufferContext) -> None:
+        self.comm_ctx = comm_ctx
+        self.data_ctx = data_ctx
+        self.grad_ctx = grad_ctx
+        backend = comm_ctx.backend
+        single = self.world_size == 1
+        need_cast = self.all_gather_dtype != self.orig_dtype
+        # all-gather input
+        if need_cast or backend.needs_registered_buffers:
+            self._ag_input = backend.alloc(self.layout.shard_numel, self.all_gather_dtype, self.device, "gather_input")
+        else:
+            self._ag_input = self._master
+        self._ag_input_version = -1
+        self._ag_input_fresh = False
+        # unsharded parameter storage
+        self._alias_data = single
+        data_flat = self._ag_input if self._alias_data else data_ctx.view(self.all_gather_dtype, self.layout.padded_numel)
+        # unsharded gradient storage
+        self._alias_grad = single and self.reduce_scatter_dtype == self.orig_dtype
+        grad_flat = self.sharded_grad_flat if self._alias_grad else grad_ctx.view(self.reduce_scatter_dtype, self.layout.padded_numel)
+        self._data_flat = data_flat
+        self._grad_flat = grad_flat
+        for sp in self.params:
+            o = self.layout.flat_offsets[sp.index]
+            view = data_flat[o : o + sp.numel].view(sp.orig_shape)
+            sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad)
+            sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape)
+            sp.sink = GradSink(self, sp.index, sp.rs_view) if sp.requires_grad else None
+            sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
+        self._register_state_dict_hooks()
+        self._lazy_inited = True
+
+    # ------------------------------------------------------------------ gather input refresh
+    def _refresh_gather_input(self) -> None:
+        """master (orig dtype) -> gather input (compute dtype), once per optimizer step."""
+        assert self._ag_input is not None
+        if self._ag_input is self._master:
+            return
+        if self._ag_input_fresh and self._ag_input_version == self._master._version:
+            return
+        with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(self._ag_input):
+            if self._master.is_cuda and self.orig_dtype == torch.float32 and self.all_gather_dtype == torch.bfloat16:
+                from .ops import kernels
+
+                kernels.cast_f32_to_bf16_(self._master, self._ag_input)
+            else:
+                self._ag_input.copy_(self._master)
+        self._ag_input_version = self._master._version
+        self._ag_input_fresh = True
+
+    def mark_gather_input_fresh(self) -> None:
+        """The fused optimizer kernel wrote the compute-dtype copy itself."""
+        self._ag_input_version = self._master._version
+        self._ag_input_fresh = True
+
+    # ------------------------------------------------------------------ unshard / reshard
+    def unshard(self, async_op: bool = False) -> None:
+        assert self._lazy_inited and self.comm_ctx is not None and self.data_ctx is not None
+        if self._is_unsharded or self._unshard_pending:
+            return
+        cc = self.comm_ctx
+        st = cc.streams
+        assert st is not None
+        logger.debug("unshard %s", self._module_fqn)
+        with record_function(self._with_fqn("YaFSDP::all_gather")):
+            if self._alias_data:
+                self._refresh_gather_input()
+                self._ag_event = None
+                self._unshard_pending = True
+                return
+            ctx = self.data_ctx
+            if ctx.owner is not None and ctx.owner is not self:
+                raise RuntimeError(
+                    f"Data buffer {ctx.index} is still owned by {ctx.owner._module_fqn!r} while {self._module_fqn!r} "
+                    "needs it: two groups that share a buffer are unsharded at the same time"
+                )
+            ctx.owner = self
+            stream = cc.get_all_gather_stream(async_op, self._training_state)
+            if stream is not st.current():
+                # the gather input may have just been produced on the compute stream (first gather after the step)
+                if not (self._ag_input_fresh and self._ag_input_version == self._master._version):
+                    st.wait_stream(stream, st.current())
+            st.wait_event(stream, ctx.release_event)
+            with st.use(stream):
+                self._refresh_gather_input()
+                assert self._ag_input is not None
+                cc.backend.all_gather(self._data_flat, self._ag_input, self.process_group)
+                self._ag_event = st.record(stream)
+            self._unshard_pending = True
+
+    def wait_for_unshard(self) -> None:
+        if not self._unshard_pending:
+            return
+        assert self.comm_ctx is not None and self.comm_ctx.streams is not None
+        self.comm_ctx.streams.wait_event(None, self._ag_event)
+        self._ag_event = None
+        for sp in self.params:
+            sp.to_unsharded()
+        self._unshard_pending = False
+        self._is_unsharded = True
+
+    def reshard(self) -> None:
+        if self._unshard_pending:
+            self.wait_for_unshard()
+        if not self._is_unsharded:
+            return
+        logger.debug("reshard %s", self._module_fqn)
+        for sp in self.params:
+            sp.to_sharded()
+        self._is_unsharded = False
+        if not self._alias_data:
+            assert self.data_ctx is not None and self.comm_ctx is not None and self.comm_ctx.streams is not None
+            self.data_ctx.release_event = self.comm_ctx.streams.record()
+            self.data_ctx.owner = None
+
+    # ------------------------------------------------------------------ forward
+    def pre_forward(self) -> None:
+        logger.debug("pre_forward %s", self._module_fqn)
+        with record_function(self._with_fqn("YaFSDP::pre_forward")):
+            self._training_state = TrainingState.FORWARD
+            self.unshard(self.unshard_async_op)
+            self.wait_for_unshard()
+
+    def post_forward(self) -> None:
+        logger.debug("post_forward %s", self._module_fqn)
+        with record_function(self._with_fqn("YaFSDP::post_forward")):
+            if not is_backward_running():  # inside backward (checkpoint recompute) the backward owns the buffer
+                if self.reshard_after_forward:
+                    self.reshard()
+                self._record_post_forward()
+            self._training_state = TrainingState.IDLE
+
+    def _record_post_forward(self) -> None:
+        assert self.comm_ctx is not None
+        idx = len(self.comm_ctx.post_forward_order)
+        self.comm_ctx.post_forward_order.append(self)
+        self._post_forward_indices.append(idx)
+
+    # ------------------------------------------------------------------ backward
+    def pre_backward(self, default_prefetch: bool = True) -> None:
+        if self._training_state == TrainingState.PRE_BACKWARD:
+            return
+        logger.debug("pre_backward %s", self._module_fqn)
+        with record_function(self._with_fqn("YaFSDP::pre_backward")):
+            self._training_state = TrainingState.PRE_BACKWARD
+            if not self._holds_grad_buffer:
+                self._sink_written = [False] * len(self.params)
+            if self.unshard_in_backward:
+                self.unshard(self.unshard_async_op)
+                self.wait_for_unshard()
+            if default_prefetch:
+                self._backward_prefetch()
+
+    def _backward_prefetch(self) -> None:
+        """Start the gather of the group that ran just before this one in forward, if it uses the other buffer."""
+        if self._training_state != TrainingState.PRE_BACKWARD or not self._post_forward_indices:
+            return
+        assert self.comm_ctx is not None
+        curr = self._post_forward_indices.pop()
+        target_idx = curr - 1
+        if target_idx < 0:
+            return
+        target = self.comm_ctx.post_forward_order[target_idx]
+        if target._alias_data or (target.data_ctx is not self.data_ctx):
+            if target.unshard_in_backward:
+                self._prefetch_unshard(target, "backward")
+
+    @staticmethod
+    def _prefetch_unshard(target: "ParamGroup", pass_type: str) -> None:
+        state = TrainingState.PRE_BACKWARD if pass_type == "backward" else TrainingState.FORWARD
+        if target._is_unsharded or target._unshard_pending:
+            return
+        ctx = target.data_ctx
+        if not target._alias_data and ctx is not None and ctx.owner is not None and ctx.owner is not target:
+            return  # the buffer is not free yet: the target gathers itself when its turn comes
+        with record_function(target._with_fqn(f"YaFSDP::{pass_type}_prefetch")):
+            old = target._training_state
+            target._training_state = state
+            target.unshard(target.unshard_async_op)
+            target._training_state = old
+
+    def _acquire_grad_buffer(self) -> None:
+        if self._holds_grad_buffer or self._alias_grad:
+            self._holds_grad_buffer = True
+            return
+        assert self.grad_ctx is not None and self.comm_ctx is not None and self.comm_ctx.streams is not None
+        ctx = self.grad_ctx
+        if ctx.owner is not None and ctx.owner is not self:
+            raise RuntimeError(
+                f"Grad buffer {ctx.index} is still owned by {ctx.owner._module_fqn!r} (gradients kept for accumulation "
+                f"without reduction) while {self._module_fqn!r} needs it; give such groups their own grad buffers"
+            )
+        self.comm_ctx.streams.wait_event(None, ctx.release_event)
+        ctx.owner = self
+        self._holds_grad_buffer = True
+
+    def post_backward(self) -> None:
+        logger.debug("post_backward %s", self._module_fqn)
+        self._training_state = TrainingState.POST_BACKWARD
+        assert self.comm_ctx is not None and self.comm_ctx.streams is not None
+        st = self.comm_ctx.streams
+        with record_function(self._with_fqn("YaFSDP::post_backward_accumulate")):
+            with_grad: list[ShardedParam] = []
+            for sp in self.params:
+                up = sp.unsharded_param
+                has_autograd_grad = up is not None and up.grad is not None
+                if has_autograd_grad or self._sink_written[sp.index]:
+                    with_grad.append(sp)
+            if not with_grad:
+                if self.reshard_after_backward:
+                    self.reshard()
+                return
+            self._acquire_grad_buffer()
+            fresh = self._alias_grad and not self._has_sharded_grads()
+            srcs, dsts_copy, dsts_add = [], [], []
+            with torch.no_grad():
+                for sp in self.params:
+                    up = sp.unsharded_param
+                    assert up is not None and sp.rs_view is not None
+                    g = up.grad
+                    if g is not None:
+                        accumulate = self._sink_written[sp.index] or (self._alias_grad and not fresh and sp.sharded_param.grad is not None)  # type: ignore[union-attr]
+                        (dsts_add if accumulate else dsts_copy).append((sp.rs_view, g))
+                        up.grad = None
+                        self._sink_written[sp.index] = True
+                    elif not self._sink_written[sp.index] and sp.requires_grad and not self._alias_grad:
+                        sp.rs_view.zero_()  # unused this step: do not reduce another layer's stale bytes
+                if dsts_copy:
+                    torch._foreach_copy_([d for d, _ in dsts_copy], [s for _, s in dsts_copy])
+                if dsts_add:
+                    torch._foreach_add_([d for d, _ in dsts_add], [s.to(d.dtype) if s.dtype != d.dtype else s for d, s in dsts_add])
+            del srcs
+        if not self.reduce_grads:
+            with record_function(self._with_fqn("YaFSDP::post_backward_reshard")):
+                if self.reshard_after_backward:
+                    self.reshard()
+            return  # keeps the grad buffer: the unsharded accumulated gradients live there
+        with record_function(self._with_fqn("YaFSDP::post_backward_reshard")):
+            if self.reshard_after_backward:
+                self.reshard()
+        with record_function(self._with_fqn("YaFSDP::post_backward_reduce")):
+            self._reduce(with_grad, st)
+
+    def _has_sharded_grads(self) -> bool:
+        return any(sp.sharded_param is not None and sp.sharded_param.grad is not None for sp in self.params)
+
+    def _reduce(self, with_grad: list[ShardedParam], st: _DeviceStreams) -> None:
+        assert self.comm_ctx is not None
+        pre, post, op, premul = gradient_divide_factors(
+            self.world_size, self.reduce_scatter_dtype, self.gradient_divide_factor, self.force_sum_reduction_for_comms
+        )
+        if op == "avg":
+            scale = 1.0 / self.world_size
+        elif op == "premul_sum":
+            scale = float(premul)  # type: ignore[arg-type]
+        else:
+            scale = 1.0
+        if post is not None and post != 1.0:
+            scale = scale / post
+        if self.world_size == 1 and self.gradient_divide_factor is not None and pre is None and post is None:
+            scale = 1.0 / self.gradient_divide_factor
+        if self._alias_grad:
+            # single rank, gradients already sit in the sharded gradient: at most a scale
+            if scale != 1.0 or (pre or 1.0) != 1.0:
+                with torch.no_grad():
+                    self.sharded_grad_flat.mul_(scale / (pre or 1.0))
+            self._finish_reduce(with_grad, None)
+            return
+        had = [sp.sharded_param.grad is not None for sp in self.params]  # type: ignore[union-attr]
+        producing = [sp.index for sp in with_grad]
+        all_fresh = not any(had)
+        all_have = all(had[i] for i in producing) and len(producing) == len([sp for sp in self.params if sp.requires_grad])
+        stream = self.comm_ctx.reduce_scatter_stream
+        st.wait_stream(stream, st.current())
+        with st.use(stream), torch.no_grad():
+            if pre is not None and pre != 1.0:
+                self._grad_flat.div_(pre)
+            dst = self.sharded_grad_flat
+            if all_fresh or all_have:
+                self.comm_ctx.backend.reduce_scatter(
+                    dst, self._grad_flat, self.process_group, scale=scale, accumulate=all_have and not all_fresh,
+                    acc_fp32=True,
+                )
+            else:
+                # mixed: some parameters accumulate, some start fresh -> reduce into the own chunk, then per parameter
+                own = self._grad_flat[self.rank * self.layout.shard_numel : (self.rank + 1) * self.layout.shard_numel]
+                self.comm_ctx.backend.reduce_scatter(own, self._grad_flat, self.process_group, scale=scale, accumulate=False)
+                for sp in with_grad:
+                    pl = sp.placement
+                    assert pl is not None
+                    src = own[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                    tgt = dst[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                    if had[sp.index]:
+                        tgt.add_(src)
+                    else:
+                        tgt.copy_(src)
+            event = st.record(stream)
+        self._finish_reduce(with_grad, event)
+
+    def _finish_reduce(self, with_grad: list[ShardedParam], event: Any) -> None:
+        self._post_reduce_event = event
+        if not self._alias_grad:
+            assert self.grad_ctx is not None
+            self.grad_ctx.release_event = event
+            self.grad_ctx.owner = None
+        self._holds_grad_buffer = False
+        self._sink_written = [False] * len(self.params)
+        for sp in with_grad:
+            assert sp.sharded_param is not None
+            _ = self.sharded_grad_flat
+            sp.sharded_param.grad = sp.sharded_grad
+
+    def finalize_backward(self) -> None:
+        assert self.comm_ctx is not None and self.comm_ctx.streams is not None
+        if self._post_reduce_event is not None:
+            self.comm_ctx.streams.wait_event(None, self._post_reduce_event)
+            self._post_reduce_event = None
+        if self._unshard_pending:
+            # a prefetch that nothing consumed (e.g. unused module): finish and release it
+            self.wait_for_unshard()
+            if self.reshard_after_backward:
+                self.reshard()
+        self._post_forward_indices.clear()
+
+    # ------------------------------------------------------------------ state dict
+    def _register_state_dict_hooks(self) -> None:
+        if getattr(self, "_sd_hooks", None):
+            return
+        handles = []
+        for m in self.modules:
+            handles.append(m.register_state_dict_pre_hook(lambda *a, **k: self._to_sharded_for_state_dict()))
+            handles.append(m._register_load_state_dict_pre_hook(lambda *a, **k: self._to_sharded_for_state_dict()))
+        self._sd_hooks = handles
+
+    def _to_sharded_for_state_dict(self) -> None:
+        if self._is_unsharded or self._unshard_pending:
+            self.reshard()
+
+    def reset_sharded_params(self) -> None:
+        """Re-derive the flat master after ``module._apply`` replaced the sharded parameters (``.to()``, ``.float()``)."""
+        new_dtype = None
+        for sp in self.params:
+            cur = sp.info.module._parameters[sp.info.param_name]
+            if cur is not sp.sharded_param and isinstance(cur, torch.Tensor):
+                new_dtype = cur.dtype
+        if new_dtype is None:
+            return
+        locals_ = []
+        for sp in self.params:
+            cur = sp.info.module._parameters[sp.info.param_name]
+            local = cur._local_tensor if isinstance(cur, RaggedShardDTensor) else cur.data._local_tensor  # type: ignore[union-attr]
+            locals_.append(local)
+        device = locals_[0].device
+        master = torch.zeros(self.layout.shard_numel, dtype=new_dtype, device=device)
+        for sp, local in zip(self.params, locals_):
+            pl = sp.placement
+            assert pl is not None
+            master[pl.shard_offset : pl.shard_offset + pl.local_numel].copy_(local)
+        self._master = master
+        self.device = device
+        self.orig_dtype = new_dtype
+        self._init_dtypes_after_apply()
+        self._sharded_grad_flat = None
+        for sp in self.params:
+            pl = sp.placement
+            assert pl is not None and sp.sharded_param is not None
+            spec = sp.sharded_param._spec.with_dtype(new_dtype)
+            sp.orig_dtype = new_dtype
+            local = master[pl.shard_offset : pl.shard_offset + pl.local_numel]
+            sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
+            sp.sharded_grad = None
+            sp.to_sharded()
+        if self._lazy_inited:
+            raise RuntimeError("changing dtype/device of a fully_shard module after its first forward is not supported")
+
+    def _init_dtypes_after_apply(self) -> None:
+        pd, rd = self.mp_policy.param_dtype, self.mp_policy.reduce_dtype
+        if rd == pd:
+            rd = None
+        if pd == self.orig_dtype:
+            pd = None
+        self.param_dtype, self.reduce_dtype = pd, rd
+        self.all_gather_dtype = pd or self.orig_dtype
+        self.reduce_scatter_dtype = rd or pd or self.orig_dtype
+
+    def _shares_nothing_data(self) -> bool:
+        return self.world_size == 1
+
+    def _shares_nothing_grad(self) -> bool:
+        return self.world_size == 1 and self.reduce_scatter_dtype == self.orig_dtype
+
+    # ------------------------------------------------------------------ misc
+    def _with_fqn(self, label: str) -> str:
+        return f"{label} ({self._module_fqn})" if self._module_fqn else label
+
+    def __repr__(self) -> str:
+        return f"ParamGroup(fqn={self._module_fqn!r}, {self.layout})"
+
+
+class RegisterPostBackwardFunction(torch.autograd.Function):
+    """Identity over the forward inputs that require grad; its backward runs once the gradients with
+    respect to the group's inputs exist, i.e. after the group's own backward: that is where the gradient
+    reduction is issued (``ya_fsdp/_param_group.py:979-992``)."""
+
+    @staticmethod
+    def forward(ctx: Any, hook: Callable[[], None], *inputs: torch.Tensor) -> Any:  # type: ignore[override]
+        ctx.hook = hook
+        ctx.set_materialize_grads(False)
+        return inputs
+
+    @staticmethod
+    def backward(ctx: Any, *grads: torch.Tensor) -> Any:  # type: ignore[override]
+        ctx.hook()
+        return (None,) + grads

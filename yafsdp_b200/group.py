@@ -586,6 +586,9 @@ class ParamGroup:
                         self._sink_written[sp.index] = True
                     elif not self._sink_written[sp.index] and sp.requires_grad and not self._alias_grad:
                         sp.rs_view.zero_()  # unused this step: do not reduce another layer's stale bytes
+                if not self._alias_grad and self.layout.padded_numel > self.layout.total_numel:
+                    # padding tail: never written by any gradient, must not carry another layer's bytes into the reduction
+                    self._grad_flat[self.layout.total_numel :].zero_()
                 if dsts_copy:
                     torch._foreach_copy_([d for d, _ in dsts_copy], [s for _, s in dsts_copy])
                 if dsts_add:

@@ -53,9 +53,11 @@ def fuse_adjacent(ts: list[torch.Tensor]) -> torch.Tensor:
     cols = first.shape[1]
     adjacent = all(t.is_contiguous() and t.shape[1] == cols and t.dtype == first.dtype for t in ts)
     if adjacent:
+        base = first.untyped_storage().data_ptr()
         end = first.data_ptr() + first.numel() * first.element_size()
         for t in ts[1:]:
-            if t.data_ptr() != end:
+            # back to back AND inside one allocation (two allocator blocks can touch by accident)
+            if t.data_ptr() != end or t.untyped_storage().data_ptr() != base:
                 adjacent = False
                 break
             end += t.numel() * t.element_size()

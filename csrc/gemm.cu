@@ -28,7 +28,8 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
-  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+  static constexpr int STAGING_BYTES = 2 * 16384;  // two [128 rows x 128 B] epilogue staging blocks for TMA stores
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
 };
 
 struct GemmArgs {
@@ -42,12 +43,13 @@ struct GemmArgs {
 template <int BLOCK_N>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         GemmArgs args) {
+                         const __grid_constant__ CUtensorMap tma_c, GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING_BYTES);
   uint64_t* full = bars;                 // [STAGES]
   uint64_t* empty = bars + STAGES;       // [STAGES]
   uint64_t* tfull = bars + 2 * STAGES;   // [2]
@@ -66,6 +68,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&tma_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -166,9 +169,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
   } else {
     // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
+    // TMEM -> registers -> 128-byte-swizzled staging block in shared memory -> TMA store (or TMA
+    // reduce-add when accumulating): full 128-byte lines leave the SM, edges are clipped by the TMA unit.
     const int q = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+    const int r_in_tile = q * 32 + lane;
+    const bool store_thread = (threadIdx.x == 64);
+    const int cols_per_chunk = args.out_f32 ? 32 : 64;
+    const int n_chunks = BLOCK_N / cols_per_chunk;
     bool alive = true;
     int lt = 0;
+    uint32_t chunk_ctr = 0;
     for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++lt) {
       int m0, n0;
       tile_coords(t, m0, n0);
@@ -176,77 +186,61 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const uint32_t acc_ph = (lt >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, 30)) { alive = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
       const float alpha = args.alpha;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < M && col < N) {
-          const bool fullw = (col + 32 <= N);
-          if (args.out_f32) {
-            float* dst = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
-            if (fullw) {
+      for (int c = 0; c < n_chunks; ++c, ++chunk_ctr) {
+        uint8_t* stg = staging + (chunk_ctr & 1) * 16384;
+        uint8_t* srow = stg + r_in_tile * 128;
+        if (store_thread) tma_store_wait_read1();  // the store that last read this block has finished reading
+        named_bar_sync(1, 128);
+        if (args.out_f32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 o;
-                o.x = alpha * __uint_as_float(r[4 * v + 0]);
-                o.y = alpha * __uint_as_float(r[4 * v + 1]);
-                o.z = alpha * __uint_as_float(r[4 * v + 2]);
-                o.w = alpha * __uint_as_float(r[4 * v + 3]);
-                float4* p = reinterpret_cast<float4*>(dst) + v;
-                if (args.accumulate) {
-                  const float4 old = *p;
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *p = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float o = alpha * __uint_as_float(r[j]);
-                if (args.accumulate) o += dst[j];
-                dst[j] = o;
-              }
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col;
-            if (fullw) {
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = alpha * __uint_as_float(r[4 * j + 0]);
+            o.y = alpha * __uint_as_float(r[4 * j + 1]);
+            o.z = alpha * __uint_as_float(r[4 * j + 2]);
+            o.w = alpha * __uint_as_float(r[4 * j + 3]);
+            *reinterpret_cast<float4*>(srow + ((j ^ (r_in_tile & 7)) << 4)) = o;
+          }
+        } else {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                float f[8];
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 64 + half * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = alpha * __uint_as_float(r[8 * v + j]);
-                uint4* p = reinterpret_cast<uint4*>(dst) + v;
-                if (args.accumulate) {
-                  const uint4 old = *p;
-                  float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
-                         a3 = unpack_bf16x2(old.w);
-                  f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y;
-                  f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
-                }
-                uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]);
-                o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]);
-                o.w = pack_bf16x2(f[6], f[7]);
-                *p = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float o = alpha * __uint_as_float(r[j]);
-                if (args.accumulate) o += __bfloat162float(dst[j]);
-                dst[j] = __float2bfloat16_rn(o);
-              }
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 0]), alpha * __uint_as_float(r[8 * j + 1]));
+              o.y = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 2]), alpha * __uint_as_float(r[8 * j + 3]));
+              o.z = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 4]), alpha * __uint_as_float(r[8 * j + 5]));
+              o.w = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 6]), alpha * __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(srow + (((half * 4 + j) ^ (r_in_tile & 7)) << 4)) = o;
             }
           }
         }
+        if (c == n_chunks - 1) {  // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(&tempty[acc]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (store_thread) {
+          const int x = n0 + c * cols_per_chunk;
+          if (x < N && m0 < M) {
+            if (args.accumulate) tma_reduce_add_2d(&tma_c, stg, x, m0);
+            else tma_store_2d(&tma_c, stg, x, m0);
+          }
+          tma_store_commit();
+        }
       }
-      tc_fence_before();
-      mbar_arrive(&tempty[acc]);
     }
+    if (store_thread) tma_store_wait0();
   }
 
   tc_fence_before();
@@ -265,7 +259,8 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long ld
                                     : yf_tensor_map_2d(A, args.K, args.M, lda, BLOCK_K, BLOCK_M, 2, 1);
   const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(B, args.N, args.K, ldb, 64, BLOCK_K, 2, 1)
                                     : yf_tensor_map_2d(B, args.K, args.N, ldb, BLOCK_K, BLOCK_N, 2, 1);
-  if (!ma || !mb) return -2;
+  const CUtensorMap* mc = yf_tensor_map_2d(args.C, args.N, args.M, args.ldc, args.out_f32 ? 32 : 64, BLOCK_M, args.out_f32 ? 4 : 2, 1);
+  if (!ma || !mb || !mc) return -2;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -277,7 +272,7 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long ld
   int sms = yf_num_sms();
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
   const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, args);
+  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, *mc, args);
   return -(int)cudaGetLastError();
 }
 

@@ -1,0 +1,226 @@
+// Peer-memory collectives over NVLink for sm_100a: pull all-gather, pull reduce-scatter with fp32
+// accumulation, and a signal-pad barrier between GPUs.  No NCCL: every rank maps every peer's buffers
+// (CUDA IPC, set up by the host side below) and the kernels load straight from peer memory with
+// system-scope relaxed loads (never through L1).  The kernels use no shared memory and few registers, so
+// their CTAs co-reside on the SMs with the persistent tcgen05 GEMM CTAs instead of taking SMs away.
+//
+// Every wait on another GPU is bounded: when the budget runs out the kernel records
+// YF_ERR_FLAG_TIMEOUT in the status word and returns.
+#include <string.h>
+
+#include "common.cuh"
+#include "yafsdp_b200.h"
+
+YF_TU_STATUS()
+
+namespace {
+
+constexpr int MAX_RANKS = 16;
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+YF_DEVINL uint4 ld_sys_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+YF_DEVINL void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+YF_DEVINL unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// out[r * shard .. (r+1) * shard) = peer_r's shard, for every r.  Rank k starts with its own shard and
+// walks the peers in the order k+1, k+2, ...: at any moment every GPU reads from a different peer.
+constexpr int AG_UNROLL = 4;
+__global__ void __launch_bounds__(512) allgather_pull_kernel(PeerPtrs in, uint4* __restrict__ out, long long shard_vec, int rank, int world) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (int d = 0; d < world; ++d) {
+    const int r = (rank + d) % world;
+    const uint4* src = reinterpret_cast<const uint4*>(in.p[r]);
+    uint4* dst = out + (long long)r * shard_vec;
+    long long i = tid;
+    for (; i + (AG_UNROLL - 1) * stride < shard_vec; i += AG_UNROLL * stride) {
+      uint4 v[AG_UNROLL];
+#pragma unroll
+      for (int u = 0; u < AG_UNROLL; ++u) v[u] = ld_sys_v4(src + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < AG_UNROLL; ++u) dst[i + u * stride] = v[u];
+    }
+    for (; i < shard_vec; i += stride) dst[i] = ld_sys_v4(src + i);
+  }
+}
+
+// dst[i] (+)= scale * sum_{r = 0..world-1} peer_r[rank * shard + i]; the sum runs in rank order on every
+// owner, in fp32, so the result is deterministic.  Wire format fp32 or bf16.
+template <bool BF16_WIRE>
+__global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs in, float* __restrict__ dst, long long shard_numel, int rank,
+                                                                  int world, float scale, int accumulate) {
+  constexpr int EPV = BF16_WIRE ? 8 : 4;  // elements per 16-byte vector on the wire
+  const long long nvec = shard_numel / EPV;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    uint4 v[MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) v[r] = ld_sys_v4(reinterpret_cast<const uint4*>(in.p[r]) + (long long)rank * nvec + i);
+    float acc[EPV];
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) {
+        if (BF16_WIRE) {
+          const float2 a = unpack_bf16x2(v[r].x), b = unpack_bf16x2(v[r].y), c = unpack_bf16x2(v[r].z), d = unpack_bf16x2(v[r].w);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+          acc[4 % EPV] += c.x; acc[5 % EPV] += c.y; acc[6 % EPV] += d.x; acc[7 % EPV] += d.y;
+        } else {
+          acc[0] += __uint_as_float(v[r].x);
+          acc[1] += __uint_as_float(v[r].y);
+          acc[2] += __uint_as_float(v[r].z);
+          acc[3] += __uint_as_float(v[r].w);
+        }
+      }
+    }
+    float4* d4 = reinterpret_cast<float4*>(dst + i * EPV);
+#pragma unroll
+    for (int h = 0; h < EPV / 4; ++h) {
+      float4 o = make_float4(acc[4 * h] * scale, acc[4 * h + 1] * scale, acc[4 * h + 2] * scale, acc[4 * h + 3] * scale);
+      if (accumulate) {
+        const float4 old = d4[h];
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      }
+      d4[h] = o;
+    }
+  }
+}
+
+// Barrier between GPUs on signal pads.  pad layout: unsigned 64-bit words [slot][MAX_RANKS]; rank k writes
+// `seq` into word [slot][k] of every rank's pad and waits until all words [slot][*] of its own pad have
+// reached `seq`.  Sequence numbers only grow, so pads are never reset.
+__global__ void signal_barrier_kernel(PeerPtrs pads, int rank, int world, int slot, unsigned long long seq, unsigned long long timeout_ns) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  unsigned long long* theirs = reinterpret_cast<unsigned long long*>(pads.p[r]) + (size_t)slot * MAX_RANKS + rank;
+  st_release_sys_u64(theirs, seq);
+  const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(pads.p[rank]) + (size_t)slot * MAX_RANKS + r;
+  const uint64_t t0 = yf_globaltimer();
+  for (uint32_t it = 0;; ++it) {
+    if (ld_acquire_sys_u64(mine) >= seq) break;
+    if ((it & 63u) == 63u) {
+      if (yf_globaltimer() - t0 > timeout_ns) {
+        yf_raise(YF_ERR_FLAG_TIMEOUT, 300 + slot);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();
+}
+
+// Wait until word `index` of a local flag array reaches `value` (bounded); and its setter.
+__global__ void flag_wait_kernel(const unsigned long long* flags, long long index, unsigned long long value, unsigned long long timeout_ns) {
+  const uint64_t t0 = yf_globaltimer();
+  for (uint32_t it = 0;; ++it) {
+    if (ld_acquire_sys_u64(flags + index) >= value) break;
+    if ((it & 63u) == 63u) {
+      if (yf_globaltimer() - t0 > timeout_ns) {
+        yf_raise(YF_ERR_FLAG_TIMEOUT, 400);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+__global__ void flag_set_kernel(unsigned long long* flags, long long index, unsigned long long value) {
+  __threadfence_system();
+  st_release_sys_u64(flags + index, value);
+}
+
+PeerPtrs to_peers(void* const* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_RANKS; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return pp;
+}
+
+}  // namespace
+
+extern "C" int yf_allgather_pull(void* const* peer_in, void* out, long long shard_bytes, int rank, int world, int n_ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || shard_bytes <= 0 || (shard_bytes % 16)) return -1;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
+  for (int r = 0; r < world; ++r)
+    if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
+  if (n_ctas <= 0) n_ctas = 2 * yf_num_sms();
+  allgather_pull_kernel<<<n_ctas, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(peer_in, world), reinterpret_cast<uint4*>(out),
+                                                                                   shard_bytes / 16, rank, world);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
+                                      int accumulate, int bf16_wire, int n_ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || shard_numel <= 0 || (shard_numel % 8)) return -1;
+  if (reinterpret_cast<uintptr_t>(dst) & 15) return -1;
+  for (int r = 0; r < world; ++r)
+    if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
+  if (n_ctas <= 0) n_ctas = 2 * yf_num_sms();
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bf16_wire)
+    reduce_scatter_pull_kernel<true><<<n_ctas, 256, 0, st>>>(to_peers(peer_in, world), dst, shard_numel, rank, world, scale, accumulate);
+  else
+    reduce_scatter_pull_kernel<false><<<n_ctas, 256, 0, st>>>(to_peers(peer_in, world), dst, shard_numel, rank, world, scale, accumulate);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || slot < 0 || seq <= 0) return -1;
+  signal_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(pads, world), rank, world, slot,
+                                                                             (unsigned long long)seq,
+                                                                             (unsigned long long)timeout_ms * 1000000ull);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream) {
+  flag_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const unsigned long long*>(flags), index,
+                                                                       (unsigned long long)value, (unsigned long long)timeout_ms * 1000000ull);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int yf_flag_set(void* flags, long long index, long long value, void* stream) {
+  flag_set_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<unsigned long long*>(flags), index,
+                                                                      (unsigned long long)value);
+  return -(int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- peer-mapped memory (CUDA IPC)
+// yf_ipc_alloc: cudaMalloc + zero + export handle (64 bytes).  yf_ipc_open: map a peer's handle into this
+// process (peer access is enabled lazily by the runtime).  Allocations live until yf_ipc_free / process exit.
+extern "C" int yf_ipc_alloc(long long nbytes, void** ptr_out, void* handle_out64) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)nbytes);
+  if (e != cudaSuccess) return -(int)e;
+  e = cudaMemset(p, 0, (size_t)nbytes);
+  if (e != cudaSuccess) return -(int)e;
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return -(int)e;
+  memcpy(handle_out64, &h, sizeof(h));
+  *ptr_out = p;
+  return 0;
+}
+extern "C" int yf_ipc_open(const void* handle64, void** ptr_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return -(int)e;
+  *ptr_out = p;
+  return 0;
+}
+extern "C" int yf_ipc_close(void* ptr) { return -(int)cudaIpcCloseMemHandle(ptr); }
+extern "C" int yf_ipc_free(void* ptr) { return -(int)cudaFree(ptr); }

@@ -44,6 +44,18 @@ int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
                 long long q_stride, long long kv_stride, long long o_stride, long long do_stride, long long dq_stride,
                 long long dkv_stride, float scale, int causal, void* stream);
 
+// ---- peer-memory collectives over NVLink (comm.cu); peer arrays are host arrays of `world` device pointers
+int yf_allgather_pull(void* const* peer_in, void* out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
+int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
+                           int accumulate, int bf16_wire, int n_ctas, void* stream);
+int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream);
+int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream);
+int yf_flag_set(void* flags, long long index, long long value, void* stream);
+int yf_ipc_alloc(long long nbytes, void** ptr_out, void* handle_out64);
+int yf_ipc_open(const void* handle64, void** ptr_out);
+int yf_ipc_close(void* ptr);
+int yf_ipc_free(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -155,10 +155,13 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_allgather_pull": [_P, _P, _L, _I, _I, _I, _P],
         "yf_reduce_scatter_pull": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P],
-        "yf_signal_barrier": [_P, _P, _I, _I, _L, _L, _P],
-        "yf_flag_wait": [_P, _L, _L, _P],
-        "yf_flag_set": [_P, _L, _P],
-        "yf_gemm_bf16_gathered": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _P, _L, _L, _L, _I, _I, _I, _I, _L, _P, _I, _P],
+        "yf_signal_barrier": [_P, _I, _I, _I, _L, _L, _P],
+        "yf_flag_wait": [_P, _L, _L, _L, _P],
+        "yf_flag_set": [_P, _L, _L, _P],
+        "yf_ipc_alloc": [_L, _P, _P],
+        "yf_ipc_open": [_P, _P],
+        "yf_ipc_close": [_P],
+        "yf_ipc_free": [_P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name, None)

@@ -1,0 +1,178 @@
+"""Peer-memory ("symmetric") collective backend: hand-written NVLink kernels instead of NCCL.
+
+Every rank allocates its communication buffers from an arena of CUDA-IPC-exported memory and maps
+every peer's arena, so a buffer at offset ``o`` of the local arena has a twin at offset ``o`` of each
+peer's arena (all ranks allocate in the same order with the same sizes).  The kernels
+(``csrc/comm.cu``) then *pull*:
+
+* all-gather: each rank copies the peers' shards straight into its local layer buffer;
+* reduce-scatter: each owner reads its chunk of every rank's fp32 gradient buffer, sums in rank
+  order with fp32 accumulation, applies the averaging factor and accumulates into the sharded gradient
+  in the same pass (reference: four separate steps, ``ya_fsdp/_collectives.py:93-218``).
+
+Cross-GPU ordering uses signal pads (sequence-numbered flags in peer memory) with bounded waits; a
+wait that runs out sets the library status word, which ``check()`` reads.
+
+This is the structure the reference gets from its optional closed-source library (registered
+buffers owned by the communication layer, in-place collectives, fp32 accumulation:
+``ya_fsdp/_param_group.py:46-69``, ``ya_fsdp/_collectives.py:66-71,163-164``), written for one
+NVSwitch-connected box.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops import kernels
+from .backends import CommBackend
+
+__all__ = ["SymmBackend", "SymmArena"]
+
+_ALIGN = 1024
+
+
+class _CudaBuffer:
+    """Expose a raw device allocation to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class SymmArena:
+    """Bump allocator over chunks of IPC-shared device memory mapped by every rank of ``group``."""
+
+    def __init__(self, device: torch.device, group: dist.ProcessGroup, chunk_bytes: int = 1 << 30):
+        self.device = device
+        self.group = group
+        self.rank = group.rank()
+        self.world = group.size()
+        self.chunk_bytes = chunk_bytes
+        self.chunks: list[tuple[int, int, list[int], torch.Tensor]] = []  # (local base, nbytes, peer bases, tensor)
+        self.offset = 0
+
+    def _new_chunk(self, nbytes: int) -> None:
+        lib = _native.lib()
+        ptr = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            rc = lib.yf_ipc_alloc(nbytes, ctypes.byref(ptr), handle)
+        if rc != 0:
+            raise RuntimeError(f"yf_ipc_alloc({nbytes}) failed with code {rc}")
+        handles: list[bytes | None] = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=self.group)
+        bases: list[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                bases.append(int(ptr.value))  # type: ignore[arg-type]
+                continue
+            hb = (ctypes.c_ubyte * 64).from_buffer_copy(h)  # type: ignore[arg-type]
+            peer = ctypes.c_void_p()
+            with torch.cuda.device(self.device):
+                rc = lib.yf_ipc_open(hb, ctypes.byref(peer))
+            if rc != 0:
+                raise RuntimeError(f"yf_ipc_open of rank {r}'s buffer failed with code {rc} (peer access over NVLink is required)")
+            bases.append(int(peer.value))  # type: ignore[arg-type]
+        tensor = torch.as_tensor(_CudaBuffer(int(ptr.value), nbytes), device=self.device)  # type: ignore[arg-type]
+        self.chunks.append((int(ptr.value), nbytes, bases, tensor))  # type: ignore[arg-type]
+        self.offset = 0
+
+    def alloc(self, nbytes: int) -> torch.Tensor:
+        nbytes = (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        if not self.chunks or self.offset + nbytes > self.chunks[-1][1]:
+            self._new_chunk(max(nbytes, self.chunk_bytes))
+        base, _, _, tensor = self.chunks[-1]
+        out = tensor[self.offset : self.offset + nbytes]
+        self.offset += nbytes
+        return out
+
+    def peer_ptrs(self, t: torch.Tensor) -> list[int]:
+        p = t.data_ptr()
+        for base, nbytes, bases, _ in self.chunks:
+            if base <= p < base + nbytes:
+                return [b + (p - base) for b in bases]
+        raise ValueError("tensor was not allocated from the symmetric arena")
+
+
+def _ptr_array(ptrs: list[int]) -> ctypes.Array:
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class SymmBackend(CommBackend):
+    name = "symm"
+    needs_registered_buffers = True
+
+    N_SLOTS = 8
+
+    def __init__(self, device: torch.device, group: dist.ProcessGroup | None):
+        if group is None or device.type != "cuda":
+            raise ValueError("the symmetric backend needs a CUDA device and a process group")
+        if group.size() > 16:
+            raise ValueError("the symmetric backend supports at most 16 ranks (one NVSwitch domain)")
+        self.device = device
+        self.group = group
+        self.rank = group.rank()
+        self.world = group.size()
+        self.arena = SymmArena(device, group, chunk_bytes=int(os.environ.get("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20)
+        self.pads = self.arena.alloc(self.N_SLOTS * 16 * 8)
+        self._pad_ptrs = _ptr_array(self.arena.peer_ptrs(self.pads))
+        self._seq = [0] * self.N_SLOTS
+        self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
+        self.ag_ctas = int(os.environ.get("YAFSDP_AG_CTAS", "0"))
+        self.rs_ctas = int(os.environ.get("YAFSDP_RS_CTAS", "0"))
+        self._ptr_cache: dict[int, ctypes.Array] = {}
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------------ memory
+    def alloc(self, numel: int, dtype: torch.dtype, device: torch.device, kind: str) -> torch.Tensor:
+        if kind == "gather_output":
+            return torch.empty(numel, dtype=dtype, device=device)  # only this rank reads or writes it
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        return self.arena.alloc(nbytes)[:nbytes].view(dtype)
+
+    def _peers(self, t: torch.Tensor) -> ctypes.Array:
+        key = t.data_ptr()
+        arr = self._ptr_cache.get(key)
+        if arr is None:
+            arr = _ptr_array(self.arena.peer_ptrs(t))
+            self._ptr_cache[key] = arr
+        return arr
+
+    # ------------------------------------------------------------------ ordering between GPUs
+    def barrier(self, slot: int = 0) -> None:
+        """All ranks' current streams meet here (device-side, bounded wait)."""
+        self._seq[slot] += 1
+        rc = _native.lib().yf_signal_barrier(self._pad_ptrs, self.rank, self.world, slot, self._seq[slot], self.timeout_ms,
+                                             torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_signal_barrier")
+
+    def step_barrier(self) -> None:
+        self.barrier(0)
+
+    # ------------------------------------------------------------------ collectives
+    def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
+        nbytes = inp.numel() * inp.element_size()
+        with torch.autograd._unsafe_preserve_version_counter(out):
+            rc = _native.lib().yf_allgather_pull(self._peers(inp), out.data_ptr(), nbytes, self.rank, self.world, self.ag_ctas,
+                                                 torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_allgather_pull")
+
+    def reduce_scatter(self, dst: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None, *, scale: float,
+                       accumulate: bool, acc_fp32: bool = True) -> None:
+        if dst.dtype != torch.float32 or inp.dtype not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError("the symmetric reduce-scatter produces fp32 from an fp32 or bf16 wire format")
+        shard = inp.numel() // self.world
+        self.barrier(1)  # every rank's gradients for this group are complete
+        rc = _native.lib().yf_reduce_scatter_pull(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                  int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
+                                                  torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_reduce_scatter_pull")
+        self.barrier(2)  # every owner has read this rank's buffer: it may be overwritten
+
+    def check(self) -> None:
+        kernels.check_status()

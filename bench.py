@@ -206,7 +206,7 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
     def step_e2e(ids_host: torch.Tensor) -> float:
         return step(ids_host).item()
 
-    backend = args.comm_backend if args.comm_backend != "auto" else "torch"
+    backend = args.comm_backend if args.comm_backend != "auto" else ("symm" if world > 1 else "none (single rank: buffers aliased)")
     return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, {"comm_backend": backend, "params": cfg.num_params()}
 
 

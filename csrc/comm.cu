@@ -37,7 +37,7 @@ YF_DEVINL unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
 // out[r * shard .. (r+1) * shard) = peer_r's shard, for every r.  Rank k starts with its own shard and
 // walks the peers in the order k+1, k+2, ...: at any moment every GPU reads from a different peer.
 constexpr int AG_UNROLL = 4;
-__global__ void __launch_bounds__(512) allgather_pull_kernel(PeerPtrs in, uint4* __restrict__ out, long long shard_vec, int rank, int world) {
+__global__ void __launch_bounds__(512, 1) allgather_pull_kernel(PeerPtrs in, uint4* __restrict__ out, long long shard_vec, int rank, int world) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   for (int d = 0; d < world; ++d) {
@@ -57,46 +57,76 @@ __global__ void __launch_bounds__(512) allgather_pull_kernel(PeerPtrs in, uint4*
 }
 
 // dst[i] (+)= scale * sum_{r = 0..world-1} peer_r[rank * shard + i]; the sum runs in rank order on every
-// owner, in fp32, so the result is deterministic.  Wire format fp32 or bf16.
-template <bool BF16_WIRE>
+// owner, in fp32, so the result is deterministic.  Wire format fp32 or bf16.  WORLD is a template parameter so
+// that the per-thread vectors stay in registers; each thread keeps about eight 16-byte peer loads in flight.
+template <bool BF16_WIRE, int WORLD>
 __global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs in, float* __restrict__ dst, long long shard_numel, int rank,
-                                                                  int world, float scale, int accumulate) {
+                                                                  float scale, int accumulate) {
   constexpr int EPV = BF16_WIRE ? 8 : 4;  // elements per 16-byte vector on the wire
+  constexpr int U = (WORLD >= 8) ? 1 : (8 / WORLD);
   const long long nvec = shard_numel / EPV;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    uint4 v[MAX_RANKS];
+  const uint4* src[WORLD];
 #pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r)
-      if (r < world) v[r] = ld_sys_v4(reinterpret_cast<const uint4*>(in.p[r]) + (long long)rank * nvec + i);
-    float acc[EPV];
+  for (int r = 0; r < WORLD; ++r) src[r] = reinterpret_cast<const uint4*>(in.p[r]) + (long long)rank * nvec;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 v[U][WORLD];
 #pragma unroll
-    for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
 #pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r) {
-      if (r < world) {
+        for (int r = 0; r < WORLD; ++r) v[u][r] = ld_sys_v4(src[r] + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) break;
+      float acc[EPV];
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
         if (BF16_WIRE) {
-          const float2 a = unpack_bf16x2(v[r].x), b = unpack_bf16x2(v[r].y), c = unpack_bf16x2(v[r].z), d = unpack_bf16x2(v[r].w);
+          const float2 a = unpack_bf16x2(v[u][r].x), b = unpack_bf16x2(v[u][r].y), c = unpack_bf16x2(v[u][r].z),
+                       d = unpack_bf16x2(v[u][r].w);
           acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
           acc[4 % EPV] += c.x; acc[5 % EPV] += c.y; acc[6 % EPV] += d.x; acc[7 % EPV] += d.y;
         } else {
-          acc[0] += __uint_as_float(v[r].x);
-          acc[1] += __uint_as_float(v[r].y);
-          acc[2] += __uint_as_float(v[r].z);
-          acc[3] += __uint_as_float(v[r].w);
+          acc[0] += __uint_as_float(v[u][r].x);
+          acc[1] += __uint_as_float(v[u][r].y);
+          acc[2] += __uint_as_float(v[u][r].z);
+          acc[3] += __uint_as_float(v[u][r].w);
         }
       }
-    }
-    float4* d4 = reinterpret_cast<float4*>(dst + i * EPV);
+      float4* d4 = reinterpret_cast<float4*>(dst + i * EPV);
 #pragma unroll
-    for (int h = 0; h < EPV / 4; ++h) {
-      float4 o = make_float4(acc[4 * h] * scale, acc[4 * h + 1] * scale, acc[4 * h + 2] * scale, acc[4 * h + 3] * scale);
-      if (accumulate) {
-        const float4 old = d4[h];
-        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      for (int h = 0; h < EPV / 4; ++h) {
+        float4 o = make_float4(acc[4 * h] * scale, acc[4 * h + 1] * scale, acc[4 * h + 2] * scale, acc[4 * h + 3] * scale);
+        if (accumulate) {
+          const float4 old = d4[h];
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        d4[h] = o;
       }
-      d4[h] = o;
     }
+  }
+}
+
+template <bool BF16_WIRE>
+int launch_rs(PeerPtrs pp, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate, int n_ctas,
+              cudaStream_t st) {
+  switch (world) {
+#define YF_RS_CASE(W)                                                                                                        \
+  case W:                                                                                                                    \
+    reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 256, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate);         \
+    return 0;
+    YF_RS_CASE(1) YF_RS_CASE(2) YF_RS_CASE(3) YF_RS_CASE(4) YF_RS_CASE(5) YF_RS_CASE(6) YF_RS_CASE(7) YF_RS_CASE(8)
+    YF_RS_CASE(16)
+#undef YF_RS_CASE
+    default:
+      return -1;
   }
 }
 
@@ -156,7 +186,8 @@ extern "C" int yf_allgather_pull(void* const* peer_in, void* out, long long shar
   if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
   for (int r = 0; r < world; ++r)
     if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
-  if (n_ctas <= 0) n_ctas = 2 * yf_num_sms();
+  // one CTA per SM: 512 threads x <= 64 registers leaves room for a persistent GEMM CTA on the same SM
+  if (n_ctas <= 0) n_ctas = yf_num_sms();
   allgather_pull_kernel<<<n_ctas, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(peer_in, world), reinterpret_cast<uint4*>(out),
                                                                                    shard_bytes / 16, rank, world);
   return -(int)cudaGetLastError();
@@ -168,12 +199,12 @@ extern "C" int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long lon
   if (reinterpret_cast<uintptr_t>(dst) & 15) return -1;
   for (int r = 0; r < world; ++r)
     if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
-  if (n_ctas <= 0) n_ctas = 2 * yf_num_sms();
+  if (n_ctas <= 0) n_ctas = yf_num_sms();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (bf16_wire)
-    reduce_scatter_pull_kernel<true><<<n_ctas, 256, 0, st>>>(to_peers(peer_in, world), dst, shard_numel, rank, world, scale, accumulate);
-  else
-    reduce_scatter_pull_kernel<false><<<n_ctas, 256, 0, st>>>(to_peers(peer_in, world), dst, shard_numel, rank, world, scale, accumulate);
+  const PeerPtrs pp = to_peers(peer_in, world);
+  const int rc = bf16_wire ? launch_rs<true>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, st)
+                           : launch_rs<false>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, st);
+  if (rc != 0) return rc;
   return -(int)cudaGetLastError();
 }
 

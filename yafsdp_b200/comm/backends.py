@@ -138,7 +138,7 @@ def make_backend(name: str | None, device: torch.device, group: dist.ProcessGrou
     """``"torch"`` (default), ``"symm"`` (peer-memory kernels; CUDA, one node) or ``"auto"``."""
     name = (name or "torch").lower()
     if name == "auto":
-        name = "torch"
+        name = "symm" if device.type == "cuda" and group is not None and 1 < group.size() <= 16 else "torch"
     if name == "torch":
         return TorchBackend()
     if name == "symm":

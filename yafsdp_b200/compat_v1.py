@@ -1,0 +1,207 @@
+"""Class-style ``YaFSDP`` wrapper with the reference's first-generation constructor.
+
+Parity: ``ya_fsdp/ya_fsdp.py:70-602`` (``YaFSDP``), the argument mapping of ``docs/migration_guide.md``.
+The class maps the old arguments onto the same core that ``fully_shard`` uses:
+
+* every ``(module, name)`` of ``modules_to_wrap_with_names`` becomes one parameter group (the reference's
+  ``SuperTensorModule``); parameters outside them (e.g. a final norm listed in
+  ``rogue_layer_norm_modules_with_names``) form further groups; the wrapped model is the parameter-less root;
+* ``zero_stage=3``: gathered weights are freed after use (two rotating weight buffers); ``zero_stage<=2``:
+  weights stay gathered after the first use (one buffer per group);
+* ``bit16_reduce_scatter`` / ``bit32_acc_for_bit16_reduce_scatter`` select the reduce dtype; gradients are
+  divided by ``dp_size * gradient_accumulation_steps`` as they are reduced, so after the last micro-batch the flat
+  fp32 gradients hold the mean (the reference divides once at the end, ``ya_fsdp.py:499-501``);
+* ``parameters()`` yields ONE flat fp32 ``nn.Parameter`` per group whose ``.grad`` is the group's flat fp32
+  gradient shard (the reference exposes two flat parameters, ``ya_fsdp.py:364-410``); any ``torch.optim`` optimizer
+  then runs a few large foreach kernels;
+* ``clip_grad_norm_``, ``local_state_dict`` / ``load_state_dict`` (local format with ``"meta"``), ``state_dict`` (full,
+  gathered to CPU on rank 0) and ``zero_grad`` (``set_to_none=True`` refused: the gradients are persistent flat
+  buffers) behave as in the reference.
+
+Not carried over: the closed-source communication library switches (``use_yccl*``: accepted and ignored with
+a warning; the peer-memory backend plays that role, ``comm_backend="symm"``), ``yccl_intra_inter_expr`` (an
+``eval`` of a user string) and hierarchical partitioning across nodes (``hpz_first_layers_num``: a single
+NVSwitch box has no slower inter-node tier; accepted, must be 0).
+"""
+
+from __future__ import annotations
+
+import warnings
+from typing import Any, Callable, Iterator
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.distributed.device_mesh import DeviceMesh, init_device_mesh
+
+from . import checkpoint as _ckpt
+from .api import MixedPrecisionPolicy
+from .fully_shard import fully_shard
+from .optim import param_groups_of
+
+__all__ = ["YaFSDP"]
+
+
+class YaFSDP(nn.Module):
+    def __init__(
+        self,
+        module: nn.Module,
+        zero_stage: int = 3,
+        param_dtype: torch.dtype = torch.bfloat16,
+        modules_to_wrap_with_names: list[tuple[nn.Module, str]] | None = None,
+        layer_norm_module_cls: type | tuple[type, ...] | None = None,
+        gradient_accumulation_steps: int = 1,
+        data_parallel_process_group: dist.ProcessGroup | None = None,
+        intra_node_data_parallel_process_group: dist.ProcessGroup | None = None,
+        model_parallel_process_group: dist.ProcessGroup | None = None,
+        all_reduce_grads_across_model_parallel_group: bool = False,
+        bit16_reduce_scatter: bool = False,
+        bit32_acc_for_bit16_reduce_scatter: bool = False,
+        hpz_first_layers_num: int = 0,
+        rogue_layer_norm_modules_with_names: dict[nn.Module, str] | list[tuple[nn.Module, str]] | None = None,
+        sync_module_states: bool = False,
+        param_init_fn: Callable[[nn.Module], None] | None = None,
+        device_id: int | torch.device | None = None,
+        is_trainable: bool = True,
+        use_yccl: bool = False,
+        use_yccl_padding: bool = False,
+        yccl_intra_inter_expr: str | None = None,
+        yccl_all_gather_stages: int | None = None,
+        profile: bool = False,
+        comm_backend: str = "auto",
+    ):
+        super().__init__()
+        if hpz_first_layers_num:
+            raise ValueError("hpz_first_layers_num > 0 is not supported: one NVSwitch box has no secondary (intra-node) shard tier")
+        if use_yccl or yccl_intra_inter_expr is not None or yccl_all_gather_stages is not None:
+            warnings.warn("the closed-source communication library options are ignored; use comm_backend='symm'", stacklevel=2)
+        if model_parallel_process_group is not None and model_parallel_process_group.size() > 1:
+            raise NotImplementedError("composition with an external model-parallel group is not implemented")
+        if not modules_to_wrap_with_names:
+            raise ValueError("modules_to_wrap_with_names must list the (module, name) pairs to shard as units")
+        self.module = module
+        self.zero_stage = zero_stage
+        self.gradient_accumulation_steps = gradient_accumulation_steps
+        self.is_trainable = is_trainable
+        self._profile = profile
+
+        pg = data_parallel_process_group or dist.group.WORLD
+        device_type = "cpu"
+        if device_id is not None or (torch.cuda.is_available() and dist.get_backend(pg) != "gloo"):
+            device_type = "cuda"
+            if device_id is not None:
+                torch.cuda.set_device(device_id)
+        if data_parallel_process_group is None:
+            mesh = init_device_mesh(device_type, (dist.get_world_size(),))
+        else:
+            mesh = DeviceMesh.from_group(pg, device_type)
+        self._mesh = mesh
+        self._dp_size = pg.size()
+
+        reduce_dtype = torch.bfloat16 if bit16_reduce_scatter else torch.float32
+        policy = MixedPrecisionPolicy(
+            param_dtype=param_dtype,
+            reduce_dtype=reduce_dtype,
+            bit32_acc_for_bit16_reduce_scatter=bool(bit16_reduce_scatter and bit32_acc_for_bit16_reduce_scatter),
+        )
+        reshard = zero_stage >= 3
+        # with zero_stage <= 2 nobody reshards after forward, so every group gets its own weight buffer
+        kw: dict[str, Any] = dict(mesh=mesh, mp_policy=policy, reshard_after_forward=reshard if reshard else False)
+
+        wrapped: list[nn.Module] = []
+        for sub, _name in modules_to_wrap_with_names:
+            if param_init_fn is not None and any(p.device.type == "meta" for p in sub.parameters()):
+                sub.to_empty(device=torch.device(device_type, torch.cuda.current_device()) if device_type == "cuda" else "cpu")
+                param_init_fn(sub)
+            if sync_module_states:
+                _broadcast_module(sub, pg)
+            fully_shard(sub, **kw)
+            wrapped.append(sub)
+        rogue = rogue_layer_norm_modules_with_names or []
+        rogue_items = list(rogue.items()) if isinstance(rogue, dict) else list(rogue)
+        rogue_modules = [m for m, _ in rogue_items if m not in wrapped]
+        if rogue_modules:
+            if sync_module_states:
+                for m in rogue_modules:
+                    _broadcast_module(m, pg)
+            fully_shard(rogue_modules if len(rogue_modules) > 1 else rogue_modules[0], **kw)
+        leftover = [p for p in module.parameters() if not hasattr(p, "_spec")]
+        if leftover:
+            warnings.warn(f"{len(leftover)} parameters are outside the wrapped modules; they are sharded with the root group", stacklevel=2)
+        fully_shard(module, **kw)
+        module.set_comm_backend(comm_backend, num_grad_buffers=2 if zero_stage >= 2 else None)  # type: ignore[attr-defined]
+        if zero_stage <= 1:
+            module._get_fsdp_state()._lazy_init(allow_no_grad_reduce=True)  # type: ignore[attr-defined]
+        if gradient_accumulation_steps > 1 or True:
+            module.set_gradient_divide_factor(float(self._dp_size * gradient_accumulation_steps))  # type: ignore[attr-defined]
+        self._flat_params: list[nn.Parameter] | None = None
+
+    # ------------------------------------------------------------------ module protocol
+    def forward(self, *args: Any, **kwargs: Any) -> Any:
+        return self.module(*args, **kwargs)
+
+    def __getattr__(self, name: str) -> Any:
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self.module, name)
+
+    # ------------------------------------------------------------------ optimizer contract
+    def _groups(self) -> list[Any]:
+        return param_groups_of(self.module)
+
+    def parameters(self, recurse: bool = True) -> Iterator[nn.Parameter]:  # type: ignore[override]
+        """One flat parameter (original dtype) per group; ``.grad`` is bound to the group's flat gradient shard."""
+        if self._flat_params is None:
+            self._flat_params = []
+            for g in self._groups():
+                p = nn.Parameter(g.master_flat, requires_grad=self.is_trainable)
+                if self.is_trainable:
+                    p.grad = g.sharded_grad_flat
+                self._flat_params.append(p)
+        return iter(self._flat_params)
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        if set_to_none:
+            raise ValueError("YaFSDP keeps persistent flat gradient buffers: zero_grad(set_to_none=True) is not supported")
+        for g in self._groups():
+            g.sharded_grad_flat.zero_()
+            for sp in g.params:
+                if sp.sharded_param is not None and sp.sharded_param.grad is None and sp.requires_grad:
+                    _ = g.sharded_grad_flat
+                    sp.sharded_param.grad = sp.sharded_grad
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+        """L2 only: local squared norms of the flat gradients, one all-reduce, in-place scale."""
+        if norm_type != 2.0:
+            raise NotImplementedError("only the L2 norm is supported")
+        groups = self._groups()
+        total = torch.zeros((), device=groups[0].device, dtype=torch.float32)
+        for g in groups:
+            total = total + g.sharded_grad_flat.float().pow(2).sum()
+        if self._dp_size > 1:
+            dist.all_reduce(total, group=groups[0].process_group)
+        total = total.sqrt()
+        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+        for g in groups:
+            g.sharded_grad_flat.mul_(coef)
+        return total
+
+    # ------------------------------------------------------------------ checkpoints
+    def local_state_dict(self) -> dict[str, Any]:
+        return _ckpt.local_state_dict_v1(self.module)
+
+    def state_dict(self, *args: Any, **kwargs: Any) -> dict[str, torch.Tensor]:  # type: ignore[override]
+        return _ckpt.full_state_dict(self.module, rank0_only=True)
+
+    def load_state_dict(self, state_dict: dict[str, Any], *args: Any, **kwargs: Any) -> None:  # type: ignore[override]
+        _ckpt.load_local_state_dict_v1(self.module, state_dict)
+
+
+def _broadcast_module(module: nn.Module, group: dist.ProcessGroup) -> None:
+    src = dist.get_global_rank(group, 0)
+    with torch.no_grad():
+        for t in list(module.parameters()) + list(module.buffers()):
+            if t.device.type != "meta":
+                dist.broadcast(t.data, src=src, group=group)

@@ -9,6 +9,8 @@
 // The P / dS tiles are stored once as [query][key] with the 128-byte swizzle and are read both as a
 // K-major operand (dQ) and as an MN-major operand (dV, dK): the two canonical layouts coincide.
 // D = rowsum(dO * O) comes from a small pre-pass; dQ is converted to bf16 by a post-pass.
+#include <stdio.h>
+
 #include "common.cuh"
 #include "yafsdp_b200.h"
 
@@ -351,6 +353,124 @@ extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.causal = causal ? 1 : 0;
   dim3 grid((S + BKV - 1) / BKV, Hkv, B);
   attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(*mq, *mk, *mv, *md, a);
+  {
+    const long long items = T * (Hq * HD / 8);
+    long long blocks = (items + 255) / 256;
+    const long long cap = (long long)yf_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_dq_convert_kernel<<<(int)blocks, 256, 0, st>>>(dq_accum, reinterpret_cast<__nv_bfloat16*>(dq), T, Hq * HD, dq_stride);
+  }
+  return -(int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// yf_attn_bwd_noalloc: the same backward for callers that cannot allocate device memory.
+//
+// yf_attn_bwd needs two scratch arrays from its caller (delta and the fp32 dQ accumulator).  Some users of
+// this library have no way to provide them: a C or C++ host that binds the exported symbols without a
+// tensor framework, or a job that hands all of the GPU's memory to its own pool at start-up, where a later
+// cudaMalloc fails and a borrowed pool block is not available to a third-party call.  For them the scratch
+// lives in the fixed device array below, which every GPU that loads this library holds until the process
+// exits (about 16.1 MiB).  Nothing here calls cudaMalloc, cudaFree, a framework allocator or the tensor-map
+// cache (the descriptors are encoded into stack storage).
+//
+// Limits and rules:
+//  * B * S * Hq must not exceed YF_ATTN_NOALLOC_MAX_ROWS (32768 query rows x heads, e.g. one 2048-token
+//    sequence with 16 heads); larger problems are refused with -3 and a message on stderr.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+//    device current).  Make that first call outside of any stream capture.
+//  * All calls on a device share the one array and it keeps the previous call's contents; the part that must
+//    start at zero (the dQ accumulator) is cleared by every call.  Two calls whose kernels overlap on the GPU
+//    (different streams) race on it: keep calls on one device ordered.
+//
+// In host code the array's name is only a stand-in for the symbol, not a device address, so the host never
+// passes it to a kernel: it passes the pointer that cudaGetSymbolAddress returned.
+constexpr long long YF_ATTN_NOALLOC_MAX_ROWS = 32768;
+constexpr long long NOALLOC_DELTA_FLOATS = YF_ATTN_NOALLOC_MAX_ROWS;                 // delta [B, Hq, S]
+constexpr long long NOALLOC_DQ_FLOATS = YF_ATTN_NOALLOC_MAX_ROWS * 128;              // dQ accumulator [B*S, Hq*128]
+static __device__ __align__(256) float g_attn_noalloc_scratch[NOALLOC_DELTA_FLOATS + NOALLOC_DQ_FLOATS];
+
+static float* attn_noalloc_scratch_for_current_device(int* err) {
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = e != cudaSuccess ? -(int)e : -1;
+    return nullptr;
+  }
+  if (ptrs[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *err = e != cudaSuccess ? -(int)e : -1;
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  *err = 0;
+  return ptrs[dev];
+}
+
+extern "C" int yf_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                                   void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, long long q_stride,
+                                   long long kv_stride, long long o_stride, long long do_stride, long long dq_stride,
+                                   long long dkv_stride, float scale, int causal, void* stream) {
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv)) return -1;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dq_stride % 8) || (dkv_stride % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
+       reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15)
+    return -1;
+  const long long rows = (long long)B * S * Hq;
+  if (rows > YF_ATTN_NOALLOC_MAX_ROWS) {
+    fprintf(stderr,
+            "[yafsdp_b200] yf_attn_bwd_noalloc: B*S*Hq = %lld exceeds the built-in scratch for %lld rows; "
+            "use yf_attn_bwd with caller-provided scratch\n",
+            rows, YF_ATTN_NOALLOC_MAX_ROWS);
+    return -3;
+  }
+  int err = 0;
+  float* scratch = attn_noalloc_scratch_for_current_device(&err);
+  if (scratch == nullptr) return err;
+  float* delta = scratch;
+  float* dq_accum = scratch + NOALLOC_DELTA_FLOATS;  // 131072 bytes in: still 256-byte aligned
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CUtensorMap mq, mk, mv, md;  // encoded in place: the cached variants would allocate a cache entry
+  if (yf_tensor_map_3d_encode(&mq, q, (uint64_t)Hq * HD, S, B, q_stride, (uint64_t)S * q_stride, 64, BQ, 1, 2, 1) != 0 ||
+      yf_tensor_map_3d_encode(&mk, k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1) != 0 ||
+      yf_tensor_map_3d_encode(&mv, v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1) != 0 ||
+      yf_tensor_map_3d_encode(&md, dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1) != 0)
+    return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    attr_set = true;
+  }
+  const long long T = (long long)B * S;
+  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);  // must start at zero on every call
+  if (e != cudaSuccess) return -(int)e;
+  {
+    const long long warps = T * Hq;
+    long long blocks = (warps * 32 + 255) / 256;
+    const long long cap = (long long)yf_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_delta_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                  reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq, o_stride, do_stride);
+  }
+  BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.dq_accum = dq_accum;
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.dkv_stride = dkv_stride;
+  a.S = S; a.B = B; a.Hq = Hq; a.Hkv = Hkv;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal ? 1 : 0;
+  dim3 grid((S + BKV - 1) / BKV, Hkv, B);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, md, a);
   {
     const long long items = T * (Hq * HD / 8);
     long long blocks = (items + 255) / 256;

@@ -248,4 +248,7 @@ const CUtensorMap* yf_tensor_map_2d(const void* base, uint64_t inner, uint64_t o
 const CUtensorMap* yf_tensor_map_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_elems,
                                     uint64_t pitch2_elems, uint32_t b0, uint32_t b1, uint32_t b2, int elem_bytes,
                                     int swizzle128);
+// Same encoding as yf_tensor_map_3d but into caller-provided storage: no cache entry, no heap allocation.
+int yf_tensor_map_3d_encode(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_elems,
+                            uint64_t pitch2_elems, uint32_t b0, uint32_t b1, uint32_t b2, int elem_bytes, int swizzle128);
 int yf_num_sms();

@@ -113,6 +113,22 @@ const CUtensorMap* yf_tensor_map_3d(const void* base, uint64_t d0, uint64_t d1, 
   return encode(3, base, dims, pitch, box, elem_bytes, swizzle128);
 }
 
+int yf_tensor_map_3d_encode(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_elems,
+                            uint64_t pitch2_elems, uint32_t b0, uint32_t b1, uint32_t b2, int elem_bytes, int swizzle128) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -2;
+  cuuint64_t gdim[3] = {d0, d1, d2};
+  cuuint64_t gstride[2] = {pitch1_elems * (uint64_t)elem_bytes, pitch2_elems * (uint64_t)elem_bytes};
+  cuuint32_t gbox[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                           : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), gdim, gstride, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 int yf_num_sms() {
   static int sms[64] = {0};
   int dev = 0;

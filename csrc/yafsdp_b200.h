@@ -44,6 +44,17 @@ int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
                 long long q_stride, long long kv_stride, long long o_stride, long long do_stride, long long dq_stride,
                 long long dkv_stride, float scale, int causal, void* stream);
 
+// No counterpart in the reference.  yf_attn_bwd for callers that cannot allocate device memory (a plain C host
+// without a tensor framework, or a job whose own pool already holds the whole GPU): the delta / dQ-accumulator
+// scratch is a fixed device array inside the library (about 16.1 MiB per GPU, held until exit), so the call takes
+// no scratch arguments and never calls cudaMalloc / cudaFree or an allocating library routine.  Refuses B*S*Hq > 32768
+// with -3.  The first call on a device resolves the array's address: make it before any stream capture.  Calls
+// on one device share the array (the part that must be zero is cleared each call); calls that overlap on the GPU race.
+int yf_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                        void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, long long q_stride, long long kv_stride,
+                        long long o_stride, long long do_stride, long long dq_stride, long long dkv_stride, float scale,
+                        int causal, void* stream);
+
 // ---- peer-memory collectives over NVLink (comm.cu); peer arrays are host arrays of `world` device pointers
 int yf_allgather_pull(void* const* peer_in, void* out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
 int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,

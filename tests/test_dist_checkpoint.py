@@ -1,0 +1,89 @@
+"""Checkpoint format, load planner and resharding across world sizes (gloo)."""
+
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+from test_dist_features import _build, _data, _loss, _shard
+
+
+def _save_worker(rank, world, path):
+    from yafsdp_b200 import checkpoint
+
+    model = _shard(_build())
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2, foreach=True)
+    for _ in range(2):
+        opt.zero_grad()
+        _loss(model, _data(rank)).backward()
+        opt.step()
+    checkpoint.save(path, model)
+    full = checkpoint.full_state_dict(model)
+    if rank == 0:
+        torch.save(full, os.path.join(path, "full_rank0.pt"))
+        # on-disk metadata: every parameter is a flat tensor with one chunk per saving rank
+        from torch.distributed.checkpoint import FileSystemReader
+
+        md = FileSystemReader(path).read_metadata().state_dict_metadata
+        entry = md["model.layers.0.a.weight"]
+        assert tuple(entry.size) == (16 * 24,) and len(entry.chunks) == world
+        assert sum(int(c.sizes[0]) for c in entry.chunks) == 16 * 24
+
+
+def _load_worker(rank, world, path):
+    from yafsdp_b200 import checkpoint
+
+    want = torch.load(os.path.join(path, "full_rank0.pt"))
+    model = _shard(_build(seed=123))  # different init: everything must come from the checkpoint
+    checkpoint.load(path, model)
+    for n, p in model.named_parameters():
+        assert torch.equal(p.full_tensor(), want[n]), n
+    # an unsharded model loads the same files through the flat-format planner
+    if rank == 0:
+        import torch.distributed.checkpoint as dcp
+
+        plain = _build(seed=7)
+        sd = {"model": plain.state_dict()}
+        dcp.load(sd, checkpoint_id=path, planner=checkpoint.RaggedLoadPlanner(), no_dist=True)
+        for n, p in plain.named_parameters():
+            assert torch.equal(p.detach(), want[n]), n
+
+
+@pytest.mark.timeout(300)
+def test_save_world2_load_world3_and_unsharded(tmp_path):
+    path = str(tmp_path / "ckpt")
+    run_distributed(_save_worker, 2, path)
+    run_distributed(_load_worker, 3, path)
+
+
+def _optim_roundtrip_worker(rank, world, path):
+    from yafsdp_b200 import checkpoint
+    from yafsdp_b200.optim import ShardedAdamW
+
+    model = _shard(_build())
+    opt = ShardedAdamW(model, lr=1e-2)
+    for _ in range(2):
+        opt.zero_grad()
+        _loss(model, _data(rank)).backward()
+        opt.step()
+    checkpoint.save(path, model, opt, extra={"step": 2})
+    ref_m = [m.clone() for m in opt.exp_avg]
+    model2 = _shard(_build(seed=5))
+    opt2 = ShardedAdamW(model2, lr=1e-2)
+    extra = checkpoint.load(path, model2, opt2, extra={"step": 0})
+    assert extra["step"] == 2 and opt2.step_count == 2
+    for a, b in zip(ref_m, opt2.exp_avg):
+        assert torch.equal(a, b)
+    # both continue identically
+    for m, o in ((model, opt), (model2, opt2)):
+        o.zero_grad()
+        _loss(m, _data(rank)).backward()
+        o.step()
+    for (n, p), (_, q) in zip(model.named_parameters(), model2.named_parameters()):
+        assert torch.equal(p._local_tensor, q._local_tensor), n
+
+
+@pytest.mark.timeout(300)
+def test_model_and_sharded_adamw_roundtrip(tmp_path):
+    run_distributed(_optim_roundtrip_worker, 2, str(tmp_path / "ckpt2"))

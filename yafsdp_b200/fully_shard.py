@@ -139,6 +139,12 @@ def fully_shard(
     state = FSDPState()
     state.init(modules, device, mp_policy, auto)
 
+    for root_m in modules:  # remember the enclosing state so that a nested module can find its root before any forward
+        for sub in root_m.modules():
+            sub_state = get_module_state(sub)
+            if sub_state is not None and sub_state is not state:
+                sub_state._outer = state
+
     managed = _managed_modules(modules, ignored_params)
     params, buffers = _managed_states(managed, ignored_params)
     _move_states_to_device(params, buffers, device)
@@ -205,7 +211,10 @@ class YaFSDPModule:
         """Gather this module's parameters now.  With ``async_op`` the gather is only enqueued and the
         returned handle's ``wait()`` (or the module's next pre-forward) finishes it."""
         state = self._get_fsdp_state()
-        state._lazy_init()
+        root = state
+        while root._outer is not None:
+            root = root._outer
+        root._lazy_init()
         g = state._param_group
         if g is not None:
             g.unshard(async_op=async_op)

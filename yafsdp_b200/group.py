@@ -305,6 +305,7 @@ class ParamGroup:
         self._holds_grad_buffer = False
         self._post_forward_indices: list[int] = []
         self._partial_reduce_pending = False
+        self._kept_after_forward = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
 
@@ -488,6 +489,8 @@ class ParamGroup:
             if not is_backward_running():  # inside backward (checkpoint recompute) the backward owns the buffer
                 if self.reshard_after_forward:
                     self.reshard()
+                else:
+                    self._kept_after_forward = True
                 self._record_post_forward()
             self._training_state = TrainingState.IDLE
 
@@ -504,6 +507,7 @@ class ParamGroup:
         logger.debug("pre_backward %s", self._module_fqn)
         with record_function(self._with_fqn("YaFSDP::pre_backward")):
             self._training_state = TrainingState.PRE_BACKWARD
+            self._kept_after_forward = False
             if not self._holds_grad_buffer:
                 self._sink_written = [False] * len(self.params)
             if self.unshard_in_backward:

@@ -136,13 +136,16 @@ class ShardedAdamW:
         """``{"state": {param_fqn: {"exp_avg", "exp_avg_sq"}}, "step": n}`` with ``RaggedShardDTensor`` moments
         (saved by ``torch.distributed.checkpoint`` in the same flat per-parameter format as the parameters)."""
         state: dict[str, Any] = {}
+        for g in self.groups:
+            g._to_sharded_for_state_dict()
+        names = {p: n for n, p in self.module.named_parameters(remove_duplicate=False)}
         for g, m, v in zip(self.groups, self.exp_avg, self.exp_avg_sq):
             for sp in g.params:
                 pl = sp.placement
                 assert pl is not None and sp.sharded_param is not None
                 spec = sp.sharded_param._spec.with_dtype(torch.float32)
                 sl = slice(pl.shard_offset, pl.shard_offset + pl.local_numel)
-                key = sp.fqn or f"{g._module_fqn}.{sp.info.param_name}"
+                key = names.get(sp.sharded_param) or sp.fqn or f"{g._module_fqn}.{sp.info.param_name}"
                 state[key] = {"exp_avg": RaggedShardDTensor(m[sl], spec), "exp_avg_sq": RaggedShardDTensor(v[sl], spec)}
         return {"state": state, "step": self.step_count, "lr": self.lr, "betas": self.betas, "eps": self.eps,
                 "weight_decay": self.weight_decay}

@@ -65,6 +65,7 @@ class FSDPState:
         self._module_fqn: str | None = None
         self._backend_name: str | None = None
         self._num_grad_buffers: int | None = None
+        self._outer: FSDPState | None = None  # state of the enclosing fully_shard module, if any
 
     # ------------------------------------------------------------------ construction
     def init(self, modules: tuple[nn.Module, ...], device: torch.device, mp_policy: MixedPrecisionPolicy,
@@ -113,6 +114,15 @@ class FSDPState:
         with record_function("YaFSDP::root_pre_forward"):
             st = self._comm_ctx.streams
             assert st is not None
+            # a previous forward that was never followed by a backward left its last groups gathered: release them
+            if self._comm_ctx.post_forward_order and not self._state_ctx.post_backward_final_callback_queued:
+                for s in self._state_ctx.all_states:
+                    g = s._param_group
+                    if g is not None and g._kept_after_forward and g.reshard_after_backward and g._training_state == TrainingState.IDLE:
+                        g.reshard()
+                        g._kept_after_forward = False
+                        g._post_forward_indices.clear()
+                self._comm_ctx.post_forward_order.clear()
             # the gathers of this step read what the optimizer step wrote on the compute stream
             if (ev := self._state_ctx.post_optim_event) is not None:
                 st.wait_event(self._comm_ctx.all_gather_stream, ev)

@@ -106,28 +106,18 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bflo
   }
 }
 
-// dx = r * (dy*w - xhat * mean(dy*w*xhat)),  dw[j] += sum_rows dy*xhat   (dw fp32, atomically accumulated)
-// Optionally dx += dres (the gradient arriving through the residual branch), fused to save a pass.
-__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                 const __nv_bfloat16* __restrict__ w,
-                                                                 const __nv_bfloat16* __restrict__ dy,
-                                                                 const float* __restrict__ rstd,
-                                                                 const __nv_bfloat16* __restrict__ dres,
-                                                                 __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
-                                                                 int T, int D) {
+// Backward in two kernels.  (1) dx = r * (dy*w - xhat * mean(dy*w*xhat)) (+ dres, the gradient arriving
+// through the residual branch, fused to save a pass): one CTA per row, the row stays in registers.
+// (2) dw[j] += sum_rows dy * xhat: a column reduction over the token dimension, tiled [64 columns x a slice of
+// rows] per CTA with one fp32 atomic per column per CTA.
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                    const __nv_bfloat16* __restrict__ w,
+                                                                    const __nv_bfloat16* __restrict__ dy,
+                                                                    const float* __restrict__ rstd,
+                                                                    const __nv_bfloat16* __restrict__ dres,
+                                                                    __nv_bfloat16* __restrict__ dx, int T, int D) {
   __shared__ float red[32];
   const int nvec = D / 8;
-  float dwacc[RN_MAXV][8];
-#pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-  float wv[RN_MAXV][8];
-#pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
-    const int v = threadIdx.x + i * RN_THREADS;
-    if (v < nvec) load8(w + v * 8, wv[i]);
-  }
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const __nv_bfloat16* xr = x + (size_t)row * D;
     const __nv_bfloat16* dyr = dy + (size_t)row * D;
@@ -138,15 +128,15 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     for (int i = 0; i < RN_MAXV; ++i) {
       const int v = threadIdx.x + i * RN_THREADS;
       if (v < nvec) {
-        float xv[8], dv[8];
+        float xv[8], dv[8], wv[8];
         load8(xr + v * 8, xv);
         load8(dyr + v * 8, dv);
+        load8(w + v * 8, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = xv[j] * r;
-          g[i][j] = dv[j] * wv[i][j];
+          g[i][j] = dv[j] * wv[j];
           dot += g[i][j] * xh[i][j];
-          dwacc[i][j] += dv[j] * xh[i][j];
         }
       }
     }
@@ -169,13 +159,41 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
       }
     }
   }
+}
+
+constexpr int RN_DW_COLS = 64;     // columns per CTA (8 threads x 8 bf16)
+constexpr int RN_DW_ROWLANES = 32; // row lanes per CTA (256 threads / 8)
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                                             const float* __restrict__ rstd, float* __restrict__ dw, int T, int D,
+                                                             int rows_per_cta) {
+  __shared__ float part[RN_DW_ROWLANES][RN_DW_COLS + 1];
+  const int c8 = threadIdx.x & 7;
+  const int rl = threadIdx.x >> 3;
+  const int col = blockIdx.x * RN_DW_COLS + c8 * 8;
+  const int row0 = blockIdx.y * rows_per_cta;
+  const int row1 = min(T, row0 + rows_per_cta);
+  float acc[8];
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
-    const int v = threadIdx.x + i * RN_THREADS;
-    if (v < nvec) {
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (col < D) {
+    for (int row = row0 + rl; row < row1; row += RN_DW_ROWLANES) {
+      float xv[8], dv[8];
+      load8(x + (size_t)row * D + col, xv);
+      load8(dy + (size_t)row * D + col, dv);
+      const float r = rstd[row];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(dw + v * 8 + j, dwacc[i][j]);
+      for (int j = 0; j < 8; ++j) acc[j] += dv[j] * xv[j] * r;
     }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[rl][c8 * 8 + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.x < RN_DW_COLS) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < RN_DW_ROWLANES; ++r) s += part[r][threadIdx.x];
+    const int c = blockIdx.x * RN_DW_COLS + threadIdx.x;
+    if (c < D) atomicAdd(dw + c, s);
   }
 }
 
@@ -501,10 +519,21 @@ extern "C" int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
                               float* dw, int T, int D, void* stream) {
   if (T <= 0 || D <= 0 || (D % 8) || D > RN_THREADS * 8 * RN_MAXV) return -1;
   if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dx) || (dres && !aligned16(dres))) return -1;
-  const int grid = T < yf_num_sms() * 2 ? T : yf_num_sms() * 2;
-  rmsnorm_bwd_kernel<<<grid, RN_THREADS, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                                 (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
-                                                                 (__nv_bfloat16*)dx, dw, T, D);
+  const int grid = T < yf_num_sms() * 8 ? T : yf_num_sms() * 8;
+  rmsnorm_bwd_dx_kernel<<<grid, RN_THREADS, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                                    (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
+                                                                    (__nv_bfloat16*)dx, T, D);
+  if (dw) {
+    const int col_blocks = (D + RN_DW_COLS - 1) / RN_DW_COLS;
+    int splits = (yf_num_sms() * 6 + col_blocks - 1) / col_blocks;  // about six CTAs per SM in total
+    const int max_splits = (T + RN_DW_ROWLANES - 1) / RN_DW_ROWLANES;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    const int rows_per_cta = (T + splits - 1) / splits;
+    dim3 g2(col_blocks, (T + rows_per_cta - 1) / rows_per_cta);
+    rmsnorm_bwd_dw_kernel<<<g2, 256, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, rstd, dw, T, D,
+                                                             rows_per_cta);
+  }
   YF_LAUNCH_RET();
 }
 extern "C" int yf_rope(void* qkv, const float* cos_sin, int T, int seq_len, long long row_stride, int col0, int n_heads,

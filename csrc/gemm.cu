@@ -9,6 +9,8 @@
 // the three GEMMs of a linear layer (Y = X W^T, dX = dY W, dW = dY^T X) run without a transpose.
 // The fp32 output mode with accumulate writes weight gradients straight into a flat fp32 gradient
 // buffer (the cast and the micro-batch accumulation of a sharded-data-parallel step).
+#include <string.h>
+
 #include "common.cuh"
 #include "yafsdp_b200.h"
 
@@ -40,11 +42,103 @@ struct GemmArgs {
   int a_mn, b_mn, out_f32, accumulate;
 };
 
+constexpr int MAX_RANKS = 16;
+
+// Arguments of the two fused compute + collective modes (both off when zero-initialised).
+//
+// gather (all-gather -> GEMM): the first `n_comm` CTAs of the grid are communication CTAs.  They pull every
+// rank's bf16 shard of the layer (peer loads over NVLink, local copy for the own shard) into the local layer
+// buffer chunk by chunk and publish a per-chunk flag; the GEMM CTAs' producer warp waits (bounded) for the
+// chunks that cover a B tile before it issues the TMA loads, so the GEMM runs while the rest of the layer
+// is still arriving, and the whole layer buffer is filled for the GEMMs that follow.
+//
+// scatter (GEMM -> reduce-scatter): the fp32 epilogue does not store C locally; every 16-byte piece goes to the
+// rank that owns its position of the flat layer gradient, into that owner's staging slot for this rank
+// (slot r of the owner's reduce buffer = contributions of rank r to the owner's shard).  The owner then sums
+// its `world` slots locally in rank order.
+struct FusedArgs {
+  // gather
+  int n_comm;
+  int world, rank;
+  int chunks_per_shard;
+  unsigned int epoch;
+  unsigned int* flags;          // [world * chunks_per_shard], device memory of this GPU
+  const void* peer_in[MAX_RANKS];
+  uint8_t* layer_buf;
+  long long shard_bytes, chunk_bytes, b_byte_off;
+  // scatter
+  int scatter;
+  void* peer_grad[MAX_RANKS];
+  long long c_flat_off, shard_numel;
+};
+
+YF_DEVINL uint4 ld_sys_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+YF_DEVINL void st_release_gpu_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+YF_DEVINL unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+YF_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// Communication role of the gather mode: chunk ids are (shard, chunk in shard); the chunks that cover B come
+// first (rotated by rank so that the ranks do not all read the same owner at the same time), then the rest.
+__device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes) {
+  const int cps = fa.chunks_per_shard;
+  const int total = fa.world * cps;
+  auto chunk_of = [&](long long byte_off) {
+    const long long r = byte_off / fa.shard_bytes;
+    const long long j = (byte_off - r * fa.shard_bytes) / fa.chunk_bytes;
+    return (int)(r * cps + j);
+  };
+  const int first = chunk_of(fa.b_byte_off);
+  const int last = chunk_of(fa.b_byte_off + b_bytes - 1);
+  const int nprio = last - first + 1;
+  const int rot = (int)(((long long)fa.rank * nprio) / fa.world);
+  for (int q = blockIdx.x; q < total; q += fa.n_comm) {
+    int id;
+    if (q < nprio) id = first + (q + rot) % nprio;
+    else id = (q - nprio < first) ? (q - nprio) : q;
+    const int r = id / cps, j = id - r * cps;
+    const long long lo = (long long)j * fa.chunk_bytes;
+    const long long hi = min(lo + fa.chunk_bytes, fa.shard_bytes);
+    if (hi > lo) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(fa.peer_in[r]) + lo);
+      uint4* dst = reinterpret_cast<uint4*>(fa.layer_buf + (long long)r * fa.shard_bytes + lo);
+      const long long nvec = (hi - lo) / 16;
+      long long i = threadIdx.x;
+      for (; i + 3 * GEMM_THREADS < nvec; i += 4 * GEMM_THREADS) {
+        uint4 v0 = ld_sys_v4(src + i), v1 = ld_sys_v4(src + i + GEMM_THREADS), v2 = ld_sys_v4(src + i + 2 * GEMM_THREADS),
+              v3 = ld_sys_v4(src + i + 3 * GEMM_THREADS);
+        dst[i] = v0; dst[i + GEMM_THREADS] = v1; dst[i + 2 * GEMM_THREADS] = v2; dst[i + 3 * GEMM_THREADS] = v3;
+      }
+      for (; i < nvec; i += GEMM_THREADS) dst[i] = ld_sys_v4(src + i);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      st_release_gpu_u32(fa.flags + id, fa.epoch);
+    }
+  }
+}
+
 template <int BLOCK_N>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         const __grid_constant__ CUtensorMap tma_c, GemmArgs args) {
+                         const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
   using Cfg = GemmCfg<BLOCK_N>;
+  if (fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
+    gather_comm_role(fa, (long long)args.N * args.K * 2);
+    return;
+  }
+  const int cta = (int)blockIdx.x - fa.n_comm;        // index among the GEMM CTAs
+  const int nctas = (int)gridDim.x - fa.n_comm;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,9 +197,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && alive; t += nctas) {
         int m0, n0;
         tile_coords(t, m0, n0);
+        if (fa.n_comm > 0) {
+          // gather mode: the rows [n0, n0 + BLOCK_N) of B must have landed in the local layer buffer
+          const long long lo = fa.b_byte_off + (long long)n0 * K * 2;
+          const long long hi = fa.b_byte_off + (long long)min(n0 + BLOCK_N, N) * K * 2 - 1;
+          const long long r_lo = lo / fa.shard_bytes, r_hi = hi / fa.shard_bytes;
+          const int c_lo = (int)(r_lo * fa.chunks_per_shard + (lo - r_lo * fa.shard_bytes) / fa.chunk_bytes);
+          const int c_hi = (int)(r_hi * fa.chunks_per_shard + (hi - r_hi * fa.shard_bytes) / fa.chunk_bytes);
+          const uint64_t t0 = yf_globaltimer();
+          for (int c = c_lo; c <= c_hi && alive; ++c) {
+            for (uint32_t spin = 0; ld_acquire_gpu_u32(fa.flags + c) != fa.epoch; ++spin) {
+              if ((spin & 63u) == 63u) {
+                if (yf_aborted() || yf_globaltimer() - t0 > YF_WAIT_NS_DEFAULT) {
+                  yf_raise(YF_ERR_FLAG_TIMEOUT, 11);
+                  alive = false;
+                  break;
+                }
+                __nanosleep(100);
+              }
+            }
+          }
+          if (!alive) break;
+          fence_proxy_async_global();  // the chunks were written with generic stores; TMA reads them through the async proxy
+        }
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -143,7 +260,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t it = 0;
       bool alive = true;
       int lt = 0;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++lt) {
+      for (int t = cta; t < num_tiles && alive; t += nctas, ++lt) {
         const int acc = lt & 1;
         const uint32_t acc_ph = (lt >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, 20)) { alive = false; break; }
@@ -179,7 +296,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     bool alive = true;
     int lt = 0;
     uint32_t chunk_ctr = 0;
-    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++lt) {
+    for (int t = cta; t < num_tiles && alive; t += nctas, ++lt) {
       int m0, n0;
       tile_coords(t, m0, n0);
       const int acc = lt & 1;
@@ -192,7 +309,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       for (int c = 0; c < n_chunks; ++c, ++chunk_ctr) {
         uint8_t* stg = staging + (chunk_ctr & 1) * 16384;
         uint8_t* srow = stg + r_in_tile * 128;
-        if (store_thread) tma_store_wait_read1();  // the store that last read this block has finished reading
+        if (store_thread && !fa.scatter) tma_store_wait_read1();  // the store that last read this block has finished reading
         named_bar_sync(1, 128);
         if (args.out_f32) {
           uint32_t r[32];
@@ -228,6 +345,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           tc_fence_before();
           mbar_arrive(&tempty[acc]);
         }
+        if (fa.scatter) {
+          // GEMM -> reduce-scatter: rows of the staged [128 x 32 fp32] block go to their owners' slots, eight lanes per
+          // 128-byte row so that every peer store is a full line
+          named_bar_sync(1, 128);
+          const int et = threadIdx.x - 64;
+#pragma unroll
+          for (int it2 = 0; it2 < 8; ++it2) {
+            const int idx = it2 * 128 + et;
+            const int row = idx >> 3, ch = idx & 7;
+            const int m = m0 + row, col = n0 + c * 32 + ch * 4;
+            if (m < M && col < N) {
+              const float4 v = *reinterpret_cast<const float4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
+              const long long f = fa.c_flat_off + (long long)m * N + col;
+              const long long o = f / fa.shard_numel;
+              const long long loc = f - o * fa.shard_numel;
+              float* dst = reinterpret_cast<float*>(fa.peer_grad[o]) + (long long)fa.rank * fa.shard_numel + loc;
+              *reinterpret_cast<float4*>(dst) = v;
+            }
+          }
+          continue;
+        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (store_thread) {
@@ -240,7 +378,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
       }
     }
-    if (store_thread) tma_store_wait0();
+    if (store_thread && !fa.scatter) tma_store_wait0();
   }
 
   tc_fence_before();
@@ -252,7 +390,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 }
 
 template <int BLOCK_N>
-int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long lda, long long ldb, int sm_limit,
+int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
                 cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N>;
   const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(A, args.M, args.K, lda, 64, BLOCK_K, 2, 1)
@@ -271,8 +409,11 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long ld
   const int num_tiles = ((args.M + BLOCK_M - 1) / BLOCK_M) * ((args.N + BLOCK_N - 1) / BLOCK_N);
   int sms = yf_num_sms();
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
-  const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, *mc, args);
+  int gemm_ctas = sms - fa.n_comm;
+  if (gemm_ctas < 1) return -1;
+  if (num_tiles < gemm_ctas) gemm_ctas = num_tiles;
+  const int grid = gemm_ctas + fa.n_comm;  // never more CTAs than SMs: the communication CTAs and the GEMM CTAs that wait on them are co-resident
+  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, *mc, args, fa);
   return -(int)cudaGetLastError();
 }
 
@@ -301,5 +442,90 @@ extern "C" int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // 128x256 tiles unless N is small or the 256-wide tiling wastes more of the last column block
   const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
-  return use256 ? launch_gemm<256>(A, B, args, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, lda, ldb, sm_limit, s);
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  return use256 ? launch_gemm<256>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, fa, lda, ldb, sm_limit, s);
+}
+
+// All-gather -> GEMM in one kernel.  C[M,N] = A[M,K] * B[N,K]^T where B (row-major, contiguous, K-major) is a
+// sub-range of the layer's flat bf16 parameter buffer that is being gathered by the same kernel:
+//   peer_in[r]  : rank r's shard (shard_bytes bytes) of the layer, peer-mapped; entry `rank` is the local shard
+//   layer_buf   : local unsharded layer buffer (world * shard_bytes bytes); B = layer_buf + b_byte_off
+//   flags/epoch : world * chunks_per_shard words of this GPU's memory; a chunk is ready when its word == epoch
+//                 (use a new epoch for every call on the same flags, never 0)
+//   n_comm      : CTAs that copy (the GEMM gets the remaining SMs)
+// On return (stream order) the whole layer buffer is filled, not only B.
+extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int a_mn,
+                                     int out_f32, void* const* peer_in, void* layer_buf, long long shard_bytes,
+                                     long long b_byte_off, int rank, int world, void* flags, unsigned int epoch,
+                                     long long chunk_bytes, int n_comm, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if ((lda % 8) || (K % 8) || (ldc % (out_f32 ? 4 : 8)) || n_comm < 1 || epoch == 0) return -1;
+  if ((shard_bytes % 16) || (chunk_bytes % 16) || chunk_bytes <= 0 || (b_byte_off % 16)) return -1;
+  if (b_byte_off < 0 || b_byte_off + (long long)N * K * 2 > shard_bytes * world) return -1;
+  const uint8_t* B = reinterpret_cast<const uint8_t*>(layer_buf) + b_byte_off;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
+  GemmArgs args;
+  args.C = C;
+  args.M = M; args.N = N; args.K = K;
+  args.ldc = ldc;
+  args.alpha = 1.f;
+  args.a_mn = a_mn ? 1 : 0;
+  args.b_mn = 0;
+  args.out_f32 = out_f32 ? 1 : 0;
+  args.accumulate = 0;
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  fa.n_comm = n_comm;
+  fa.world = world; fa.rank = rank;
+  fa.chunk_bytes = chunk_bytes;
+  fa.chunks_per_shard = (int)((shard_bytes + chunk_bytes - 1) / chunk_bytes);
+  fa.epoch = epoch;
+  fa.flags = reinterpret_cast<unsigned int*>(flags);
+  for (int r = 0; r < world; ++r) {
+    if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
+    fa.peer_in[r] = peer_in[r];
+  }
+  fa.layer_buf = reinterpret_cast<uint8_t*>(layer_buf);
+  fa.shard_bytes = shard_bytes;
+  fa.b_byte_off = b_byte_off;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
+  return use256 ? launch_gemm<256>(A, B, args, fa, lda, K, 0, s) : launch_gemm<128>(A, B, args, fa, lda, K, 0, s);
+}
+
+// GEMM -> reduce-scatter in one kernel.  dW[M,N] = A * B^T in fp32 is not stored locally: each 16-byte piece is
+// pushed into the staging slot `rank` of the rank that owns its position c_flat_off + m*N + n of the flat layer
+// gradient (peer_grad[o] = base of owner o's reduce buffer, laid out as `world` slots of shard_numel floats).
+// shard_numel must be a multiple of 4 and N a multiple of 4.  The owners sum their slots afterwards
+// (yf_reduce_scatter_pull on local slot pointers) once every rank's pushes are complete.
+extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int a_mn,
+                                    int b_mn, float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel,
+                                    int rank, int world, int sm_limit, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if ((lda % 8) || (ldb % 8) || (N % 4) || (shard_numel % 4) || (c_flat_off % 4) || c_flat_off < 0) return -1;
+  if (c_flat_off + (long long)M * N > shard_numel * world) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return -1;
+  GemmArgs args;
+  args.C = peer_grad[rank];  // only used to build a (unused) store descriptor
+  args.M = M; args.N = N; args.K = K;
+  args.ldc = N;
+  args.alpha = alpha;
+  args.a_mn = a_mn ? 1 : 0;
+  args.b_mn = b_mn ? 1 : 0;
+  args.out_f32 = 1;
+  args.accumulate = 0;
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  fa.scatter = 1;
+  fa.world = world; fa.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;
+    fa.peer_grad[r] = peer_grad[r];
+  }
+  fa.c_flat_off = c_flat_off;
+  fa.shard_numel = shard_numel;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
+  return use256 ? launch_gemm<256>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, fa, lda, ldb, sm_limit, s);
 }

@@ -16,6 +16,14 @@ int yf_status_read(int* code, int* site, int clear);
 int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                  long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit, void* stream);
 
+// fused all-gather -> GEMM and GEMM -> reduce-scatter (same kernel, see gemm.cu for the argument contracts)
+int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int a_mn, int out_f32,
+                          void* const* peer_in, void* layer_buf, long long shard_bytes, long long b_byte_off, int rank, int world,
+                          void* flags, unsigned int epoch, long long chunk_bytes, int n_comm, void* stream);
+int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int a_mn, int b_mn,
+                         float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel, int rank, int world,
+                         int sm_limit, void* stream);
+
 // ---- memory-bound kernels (elementwise.cu)
 int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream);
 int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,

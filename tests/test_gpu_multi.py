@@ -119,3 +119,72 @@ def _train_worker(rank, world):
 
 def test_training_symm_backend_matches_nccl_backend():
     _run(_train_worker, _world())
+
+
+def _fused_worker(rank, world):
+    """All-gather -> GEMM and GEMM -> reduce-scatter fused kernels against NCCL + the plain GEMM."""
+    import ctypes
+
+    import torch.distributed as dist
+    from yafsdp_b200.comm.symm import SymmBackend, _ptr_array
+    from yafsdp_b200.ops import kernels
+
+    dev = torch.device("cuda", rank)
+    be = SymmBackend(dev, dist.group.WORLD)
+    torch.manual_seed(100 + rank)
+    # ---- a "layer": [pad 4096 | B: n x k | tail], sharded evenly; deliberately not aligned to rows or tiles
+    n, k, m = 1280, 512, 384
+    head, tail = 4096 + 8 * 7, 8 * 1001
+    total = head + n * k + tail
+    total = (total + world * 8 - 1) // (world * 8) * (world * 8)
+    shard = total // world
+    full = torch.randn(total, device=dev).bfloat16()
+    dist.broadcast(full, 0)
+    inp = be.alloc(shard, torch.bfloat16, dev, "gather_input")
+    inp.copy_(full[rank * shard : (rank + 1) * shard])
+    layer_buf = torch.zeros(total, device=dev, dtype=torch.bfloat16)
+    flags = torch.zeros(4096, device=dev, dtype=torch.int32)
+    a = torch.randn(m, k, device=dev).bfloat16()
+    torch.cuda.synchronize()
+    be.step_barrier()
+    for epoch in (1, 2):
+        layer_buf.zero_()
+        out = kernels.gemm_gathered(a, n, k, peer_in=be._peers(inp), layer_buf=layer_buf, shard_bytes=shard * 2, b_byte_off=head * 2,
+                                    rank=rank, world=world, flags=flags, epoch=epoch, chunk_bytes=64 * 1024, n_comm=8)
+        torch.cuda.synchronize()
+        assert torch.equal(layer_buf, full), "layer buffer is not the all-gather of the shards"
+        ref = a.float() @ full[head : head + n * k].view(n, k).float().t()
+        assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    kernels.check_status()
+    # ---- GEMM -> reduce-scatter: dW = dy^T x of this rank's tokens, pushed to the owners, summed there
+    t_tok, rows, cols = 256, 640, 384
+    flat_off = 8 * 13
+    ptotal = flat_off + rows * cols + 8 * 5
+    ptotal = (ptotal + world * 8 - 1) // (world * 8) * (world * 8)
+    pshard = ptotal // world
+    dy = torch.randn(t_tok, rows, device=dev).bfloat16()
+    x = torch.randn(t_tok, cols, device=dev).bfloat16()
+    gbuf = be.alloc(ptotal, torch.float32, dev, "reduce_input")  # read as `world` slots of pshard floats
+    gbuf.zero_()
+    torch.cuda.synchronize()
+    be.barrier(3)
+    kernels.gemm_scatter(dy, x, a_mn_major=True, b_mn_major=True, peer_grad=be._peers(gbuf), c_flat_off=flat_off, shard_numel=pshard,
+                         rank=rank, world=world)
+    be.barrier(3)  # everybody's pushes have landed
+    base = gbuf.data_ptr()
+    local_slots = _ptr_array([base + (r - rank) * pshard * 4 for r in range(world)])  # the pull kernel adds rank * shard
+    got = torch.zeros(pshard, device=dev, dtype=torch.float32)
+    rc = kernels._native.lib().yf_reduce_scatter_pull(local_slots, got.data_ptr(), pshard, rank, world, 1.0 / world, 0, 0, 0,
+                                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    local_dw = torch.zeros(ptotal, device=dev, dtype=torch.float32)
+    local_dw[flat_off : flat_off + rows * cols] = (dy.float().t() @ x.float()).reshape(-1)
+    want = torch.empty(pshard, device=dev, dtype=torch.float32)
+    dist.reduce_scatter_tensor(want, local_dw, op=dist.ReduceOp.AVG)
+    torch.cuda.synchronize()
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-1), (got - want).abs().max().item()
+    kernels.check_status()
+
+
+def test_fused_gather_gemm_and_gemm_scatter():
+    _run(_fused_worker, _world())

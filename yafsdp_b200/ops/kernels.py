@@ -10,6 +10,7 @@ error, and the autograd-level ops in :mod:`yafsdp_b200.ops.functional` choose be
 from __future__ import annotations
 
 import ctypes
+from typing import Any
 
 import torch
 
@@ -99,6 +100,37 @@ def gemm(
     )
     _check(rc, "yf_gemm_bf16")
     return out
+
+
+def gemm_gathered(a: torch.Tensor, n: int, k: int, *, peer_in: Any, layer_buf: torch.Tensor, shard_bytes: int, b_byte_off: int,
+                  rank: int, world: int, flags: torch.Tensor, epoch: int, chunk_bytes: int = 1 << 20, n_comm: int = 16,
+                  out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, a_mn_major: bool = False) -> torch.Tensor:
+    """All-gather -> GEMM in one kernel: ``out = A @ B^T`` where ``B [n, k]`` (bf16, contiguous) starts ``b_byte_off`` bytes
+    into ``layer_buf``, which the same kernel fills from every rank's shard (``peer_in``: ctypes array of ``world`` peer
+    pointers).  ``flags``: int32 tensor with one word per chunk; pass a fresh non-zero ``epoch`` per call."""
+    m = a.shape[1] if a_mn_major else a.shape[0]
+    if out is None:
+        out = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    cps = (shard_bytes + chunk_bytes - 1) // chunk_bytes
+    assert flags.dtype == torch.int32 and flags.numel() >= world * cps
+    rc = _native.lib().yf_gemm_bf16_gathered(
+        a.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), out.stride(0), int(a_mn_major), int(out.dtype == torch.float32),
+        peer_in, layer_buf.data_ptr(), shard_bytes, b_byte_off, rank, world, flags.data_ptr(), epoch, chunk_bytes, n_comm, _stream())
+    _check(rc, "yf_gemm_bf16_gathered")
+    return out
+
+
+def gemm_scatter(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool, b_mn_major: bool, peer_grad: Any, c_flat_off: int,
+                 shard_numel: int, rank: int, world: int, alpha: float = 1.0, sm_limit: int = 0) -> None:
+    """GEMM -> reduce-scatter push: the fp32 product goes piece by piece to the owners' staging slots for this rank
+    (``peer_grad``: ctypes array of every rank's reduce-buffer base); nothing is stored locally."""
+    m = a.shape[1] if a_mn_major else a.shape[0]
+    n = b.shape[1] if b_mn_major else b.shape[0]
+    k = a.shape[0] if a_mn_major else a.shape[1]
+    rc = _native.lib().yf_gemm_bf16_scatter(a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0), b.stride(0), int(a_mn_major),
+                                            int(b_mn_major), float(alpha), peer_grad, c_flat_off, shard_numel, rank, world,
+                                            int(sm_limit), _stream())
+    _check(rc, "yf_gemm_bf16_scatter")
 
 
 # --------------------------------------------------------------------------------------- norms etc.

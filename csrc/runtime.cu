@@ -48,8 +48,15 @@ std::mutex g_map_mu;
 // values are heap blocks that are never moved or freed: kernels receive them by value, callers by pointer
 std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 
-std::mutex g_status_mu;
-std::vector<yf_status_fn> g_status_fns;
+// function-local statics: the per-file registrars run during static initialisation, possibly before this file's globals
+std::mutex& status_mu() {
+  static std::mutex m;
+  return m;
+}
+std::vector<yf_status_fn>& status_fns() {
+  static std::vector<yf_status_fn> v;
+  return v;
+}
 
 const CUtensorMap* encode(int rank, const void* base, const uint64_t* dims, const uint64_t* pitch_elems,
                           const uint32_t* box, int elem_bytes, int swizzle128) {
@@ -143,14 +150,14 @@ int yf_num_sms() {
 }
 
 void yf_register_status(yf_status_fn fn) {
-  std::lock_guard<std::mutex> lk(g_status_mu);
-  g_status_fns.push_back(fn);
+  std::lock_guard<std::mutex> lk(status_mu());
+  status_fns().push_back(fn);
 }
 
 extern "C" int yf_status_read(int* code, int* site, int clear) {
   int first = 0, first_site = 0;
-  std::lock_guard<std::mutex> lk(g_status_mu);
-  for (yf_status_fn fn : g_status_fns) {
+  std::lock_guard<std::mutex> lk(status_mu());
+  for (yf_status_fn fn : status_fns()) {
     int v[4] = {0, 0, 0, 0};
     int e = fn(v, clear);
     if (e != 0) return -e;
@@ -162,6 +169,13 @@ extern "C" int yf_status_read(int* code, int* site, int clear) {
   if (code) *code = first;
   if (site) *site = first_site;
   return 0;
+}
+
+// Plain device-to-device copy on a stream (the copy engines do the work; used for peer-to-peer transport so that
+// bulk NVLink traffic takes no SM away from the GEMMs).
+extern "C" int yf_memcpy_async(void* dst, const void* src, long long nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  return -(int)cudaMemcpyAsync(dst, src, (size_t)nbytes, cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int yf_version() { return 1; }

@@ -70,6 +70,7 @@ int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_num
 int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream);
 int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream);
 int yf_flag_set(void* flags, long long index, long long value, void* stream);
+int yf_memcpy_async(void* dst, const void* src, long long nbytes, void* stream);
 int yf_ipc_alloc(long long nbytes, void** ptr_out, void* handle_out64);
 int yf_ipc_open(const void* handle64, void** ptr_out);
 int yf_ipc_close(void* ptr);

@@ -160,6 +160,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_signal_barrier": [_P, _I, _I, _I, _L, _L, _P],
         "yf_flag_wait": [_P, _L, _L, _L, _P],
         "yf_flag_set": [_P, _L, _L, _P],
+        "yf_memcpy_async": [_P, _P, _L, _P],
         "yf_ipc_alloc": [_L, _P, _P],
         "yf_ipc_open": [_P, _P],
         "yf_ipc_close": [_P],

@@ -122,9 +122,14 @@ class SymmBackend(CommBackend):
         self._pad_ptrs = _ptr_array(self.arena.peer_ptrs(self.pads))
         self._seq = [0] * self.N_SLOTS
         self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
+        # "ce": bulk peer transfers run on the copy engines (one cudaMemcpyAsync per peer) and only the reduction is a
+        # kernel, so communication takes no SM from the GEMMs; "sm": the pull kernels do the transfers
+        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce").lower()
+        self._staging: torch.Tensor | None = None
         self.ag_ctas = int(os.environ.get("YAFSDP_AG_CTAS", "0"))
         self.rs_ctas = int(os.environ.get("YAFSDP_RS_CTAS", "0"))
         self._ptr_cache: dict[int, ctypes.Array] = {}
+        self._int_ptr_cache: dict[int, list[int]] = {}
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -157,6 +162,20 @@ class SymmBackend(CommBackend):
     # ------------------------------------------------------------------ collectives
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
         nbytes = inp.numel() * inp.element_size()
+        if self.transport == "ce":
+            lib = _native.lib()
+            stream = torch.cuda.current_stream().cuda_stream
+            peers = self.arena.peer_ptrs(inp) if inp.data_ptr() not in self._int_ptr_cache else self._int_ptr_cache[inp.data_ptr()]
+            self._int_ptr_cache[inp.data_ptr()] = peers
+            base = out.data_ptr()
+            with torch.autograd._unsafe_preserve_version_counter(out):
+                for d in range(self.world):
+                    r = (self.rank + d) % self.world
+                    rc = lib.yf_memcpy_async(base + r * nbytes, peers[r], nbytes, stream)
+                    if rc != 0:
+                        raise RuntimeError(f"peer copy from rank {r} failed with code {rc}")
+            kernels._launches += self.world
+            return
         with torch.autograd._unsafe_preserve_version_counter(out):
             rc = _native.lib().yf_allgather_pull(self._peers(inp), out.data_ptr(), nbytes, self.rank, self.world, self.ag_ctas,
                                                  torch.cuda.current_stream().cuda_stream)
@@ -168,9 +187,34 @@ class SymmBackend(CommBackend):
             raise NotImplementedError("the symmetric reduce-scatter produces fp32 from an fp32 or bf16 wire format")
         shard = inp.numel() // self.world
         self.barrier(1)  # every rank's gradients for this group are complete
-        rc = _native.lib().yf_reduce_scatter_pull(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                                  int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
-                                                  torch.cuda.current_stream().cuda_stream)
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.transport == "ce":
+            # copy engines bring every peer's chunk for this rank into local staging slots; a local kernel sums them
+            esz = inp.element_size()
+            need = self.world * shard * esz
+            if self._staging is None or self._staging.numel() < need:
+                self._staging = torch.empty(need, dtype=torch.uint8, device=self.device)
+            peers = self._int_ptr_cache.get(inp.data_ptr())
+            if peers is None:
+                peers = self.arena.peer_ptrs(inp)
+                self._int_ptr_cache[inp.data_ptr()] = peers
+            lib = _native.lib()
+            sbase = self._staging.data_ptr()
+            srcs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    srcs.append(inp.data_ptr())  # own chunk is read in place
+                    continue
+                rc = lib.yf_memcpy_async(sbase + r * shard * esz, peers[r] + self.rank * shard * esz, shard * esz, stream)
+                if rc != 0:
+                    raise RuntimeError(f"peer copy from rank {r} failed with code {rc}")
+                srcs.append(sbase + r * shard * esz - self.rank * shard * esz)  # the kernel adds rank * shard
+            kernels._launches += self.world - 1
+            rc = lib.yf_reduce_scatter_pull(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                            int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas, stream)
+        else:
+            rc = _native.lib().yf_reduce_scatter_pull(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                      int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas, stream)
         kernels._check(rc, "yf_reduce_scatter_pull")
         self.barrier(2)  # every owner has read this rank's buffer: it may be overwritten
 

@@ -107,8 +107,9 @@ class BufferContext:
 
 
 class CommContext:
-    """Streams shared by all groups of one root: one high-priority side stream carries both the
-    all-gathers and the reduce-scatters (``ya_fsdp/_param_group.py:74-101``)."""
+    """Streams shared by all groups of one root.  The reference runs all-gathers and reduce-scatters on ONE
+    high-priority side stream (``ya_fsdp/_param_group.py:74-101``); here they get a stream each, so a backward
+    prefetch is never queued behind the previous layer's reduction and its cross-GPU barriers."""
 
     def __init__(self) -> None:
         self.streams: _DeviceStreams | None = None
@@ -120,7 +121,7 @@ class CommContext:
     def lazy_init(self, device: torch.device, backend: CommBackend | None = None) -> None:
         self.streams = _DeviceStreams(device)
         self.all_gather_stream = self.streams.new_stream(priority=-1)
-        self.reduce_scatter_stream = self.all_gather_stream
+        self.reduce_scatter_stream = self.streams.new_stream(priority=-1)
         if backend is not None:
             self.backend = backend
 

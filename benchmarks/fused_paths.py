@@ -85,7 +85,7 @@ def main() -> None:
     def fused_ag_gemm():
         epoch[0] += 1
         kernels.gemm_gathered(x, 3 * d, d, peer_in=be._peers(inp), layer_buf=layer, shard_bytes=shard * 2, b_byte_off=qkv_off * 2,
-                              rank=rank, world=world, flags=flags, epoch=epoch[0], chunk_bytes=1 << 20, n_comm=int(os.environ.get("YF_NCOMM", "20")),
+                              rank=rank, world=world, flags=flags, epoch=epoch[0], chunk_bytes=1 << 20, n_comm=int(os.environ.get("YF_NCOMM", "32")),
                               out=out)
 
     t_ag = timed(lambda: be.all_gather(layer, inp, None), dev)
@@ -126,7 +126,40 @@ def main() -> None:
             view = gbuf[off : off + dy.shape[1] * xx.shape[1]].view(dy.shape[1], xx.shape[1])
             kernels.gemm(dy, xx, a_mn_major=True, b_mn_major=True, out=view)
 
+    def scatter_only():
+        for dy, xx, off in acts.values():
+            kernels.gemm_scatter(dy, xx, a_mn_major=True, b_mn_major=True, peer_grad=be._peers(gbuf), c_flat_off=off, shard_numel=shard,
+                                 rank=rank, world=world)
+
+    # steady state of a backward pass: the reduction of layer l runs on a side stream under the GEMMs of layer l+1
+    side = torch.cuda.Stream()
+    n_layers = 4
+
+    def pipelined(fused: bool):
+        def run():
+            for _ in range(n_layers):
+                scatter_only() if fused else dw_only()
+                ev = torch.cuda.Event()
+                ev.record()
+                with torch.cuda.stream(side):
+                    side.wait_event(ev)
+                    if fused:
+                        be.barrier(1)
+                        kernels._native.lib().yf_reduce_scatter_pull(local_slots, dst.data_ptr(), shard, rank, world, 1.0 / world, 0, 0, 0,
+                                                                     side.cuda_stream)
+                        be.barrier(2)
+                    else:
+                        be.reduce_scatter(dst, gbuf, None, scale=1.0 / world, accumulate=False)
+                    done = torch.cuda.Event()
+                    done.record()
+                torch.cuda.current_stream().wait_event(done) if False else None
+            torch.cuda.current_stream().wait_stream(side)
+        return run
+
     t_dw = timed(dw_only, dev)
+    t_scatter = timed(scatter_only, dev)
+    t_pipe_unf = timed(pipelined(False), dev) / n_layers
+    t_pipe_fus = timed(pipelined(True), dev) / n_layers
     t_rs = timed(lambda: be.reduce_scatter(dst, gbuf, None, scale=1.0 / world, accumulate=False), dev)
     t_unf2 = timed(unfused_dw_rs, dev)
     t_fus2 = timed(fused_dw_rs, dev)
@@ -139,7 +172,10 @@ def main() -> None:
             "ag_gemm": {"all_gather_ms": round(t_ag, 4), "gemm_ms": round(t_gemm, 4), "unfused_ms": round(t_unf, 4), "fused_ms": round(t_fus, 4),
                         "roofline_ms": round(roof_ag, 4), "fused_fraction_of_roofline": round(roof_ag / t_fus, 3),
                         "unfused_fraction_of_roofline": round(roof_ag / t_unf, 3)},
-            "gemm_rs": {"dw_gemms_ms": round(t_dw, 4), "reduce_scatter_ms": round(t_rs, 4), "unfused_ms": round(t_unf2, 4), "fused_ms": round(t_fus2, 4),
+            "gemm_rs": {"dw_gemms_ms": round(t_dw, 4), "scatter_gemms_ms": round(t_scatter, 4),
+                        "scatter_gemms_fraction_of_roofline": round(roof_rs / t_scatter, 3),
+                        "pipelined_per_layer_unfused_ms": round(t_pipe_unf, 4), "pipelined_per_layer_fused_ms": round(t_pipe_fus, 4),
+                        "pipelined_fused_fraction_of_roofline": round(roof_rs / t_pipe_fus, 3), "reduce_scatter_ms": round(t_rs, 4), "unfused_ms": round(t_unf2, 4), "fused_ms": round(t_fus2, 4),
                         "roofline_ms": round(roof_rs, 4), "fused_fraction_of_roofline": round(roof_rs / t_fus2, 3),
                         "unfused_fraction_of_roofline": round(roof_rs / t_unf2, 3)},
         }))

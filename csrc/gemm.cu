@@ -113,10 +113,13 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes) {
       uint4* dst = reinterpret_cast<uint4*>(fa.layer_buf + (long long)r * fa.shard_bytes + lo);
       const long long nvec = (hi - lo) / 16;
       long long i = threadIdx.x;
-      for (; i + 3 * GEMM_THREADS < nvec; i += 4 * GEMM_THREADS) {
-        uint4 v0 = ld_sys_v4(src + i), v1 = ld_sys_v4(src + i + GEMM_THREADS), v2 = ld_sys_v4(src + i + 2 * GEMM_THREADS),
-              v3 = ld_sys_v4(src + i + 3 * GEMM_THREADS);
-        dst[i] = v0; dst[i + GEMM_THREADS] = v1; dst[i + 2 * GEMM_THREADS] = v2; dst[i + 3 * GEMM_THREADS] = v3;
+      constexpr int CU = 16;  // 16-byte loads in flight per thread: 192 x 16 x 16 B = 48 KB per CTA
+      for (; i + (CU - 1) * GEMM_THREADS < nvec; i += CU * GEMM_THREADS) {
+        uint4 v[CU];
+#pragma unroll
+        for (int u = 0; u < CU; ++u) v[u] = ld_sys_v4(src + i + u * GEMM_THREADS);
+#pragma unroll
+        for (int u = 0; u < CU; ++u) dst[i + u * GEMM_THREADS] = v[u];
       }
       for (; i < nvec; i += GEMM_THREADS) dst[i] = ld_sys_v4(src + i);
     }

@@ -23,7 +23,7 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int ATOM = 16384;
 constexpr int TILE = 2 * ATOM;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // producer warp, MMA warp, eight softmax / epilogue warps
 constexpr int BWD_SMEM = 1024 + 6 * TILE + 256;
 
 struct BwdArgs {
@@ -84,9 +84,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 128);
+    mbar_init(dq_read, 256);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -159,8 +159,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
     }
   } else {
+    // eight warps: warp w owns TMEM lanes [32*(w%4), +32) (one query row per thread) and, of the four 32-column
+    // chunks of every tile, the two of its half ((w-2)/4): two threads share a row and split its columns
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const int c_begin = ((warp - 2) >> 2) * 2, c_end = c_begin + 2;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = args.scale_log2;
     bool alive = true;
@@ -177,7 +180,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!mbar_wait(sdp_full, it & 1, 220)) { alive = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t rs[32], rp[32];
         tmem_ld32(tS + lane_off + c * 32, rs);
         tmem_ld32(tdP + lane_off + c * 32, rp);
@@ -209,7 +212,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_after();
       float* dq_row = args.dq_accum + ((long long)b * args.S + qrow) * ((long long)args.Hq * HD) + h * HD;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tmem_ld32(tS + lane_off + c * 32, r);
         tmem_ld_wait();
@@ -232,7 +235,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         __nv_bfloat16* dst = (which == 0 ? args.dv : args.dk) + off;
         const uint32_t tsrc = (which == 0 ? tdV : tdK) + lane_off;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t r[32];
           tmem_ld32(tsrc + c * 32, r);
           tmem_ld_wait();

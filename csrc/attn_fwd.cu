@@ -3,9 +3,10 @@
 // One CTA per (128-row query tile, query head, sequence).  Roles:
 //   warp 0     TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
 //   warp 1     MMA issuer:   S = Q K^T (tcgen05, fp32 in TMEM, double-buffered) and O_j = P V
-//   warps 2-5  softmax:      one query row per thread (TMEM lane == row, so no shuffles): online max /
-//                            sum, P written as bf16 into 128-byte-swizzled shared memory (the A operand
-//                            of the second MMA), running output kept in registers and rescaled.
+//   warps 2-9  softmax:      two threads per query row (TMEM lane == row; the pair splits the 128 key columns and
+//                            the 128 output columns, and exchanges its partial row maximum through shared
+//                            memory): online max / sum, P written as bf16 into 128-byte-swizzled shared memory
+//                            (the A operand of the second MMA), running output kept in registers and rescaled.
 // Inputs are read in place from the fused QKV projection output ([tokens, (Hq+2Hkv)*128], row pitch
 // given), so no head transposes are materialised.  Writes O (bf16) and the log-sum-exp per row (fp32).
 #include "common.cuh"
@@ -20,8 +21,8 @@ constexpr int BQ = 128;        // query rows per CTA
 constexpr int BKV = 128;       // keys per tile
 constexpr int ATOM = 16384;    // bytes of one [128 rows x 64 bf16] swizzled block
 constexpr int TILE = 2 * ATOM; // one 128x128 bf16 tile
-constexpr int FWD_THREADS = 192;
-constexpr int FWD_SMEM = 1024 + TILE /*Q*/ + 2 * 2 * TILE /*K,V x2 stages*/ + TILE /*P*/ + 256;
+constexpr int FWD_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
+constexpr int FWD_SMEM = 1024 + TILE /*Q*/ + 2 * 2 * TILE /*K,V x2 stages*/ + TILE /*P*/ + 256 + 3072 /*row max / sum exchange*/;
 
 struct FwdArgs {
   __nv_bfloat16* out;
@@ -50,6 +51,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint64_t* p_ready = bars + 9;         // 1
   uint64_t* o_full = bars + 10;         // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  float* xmax = reinterpret_cast<float*>(bars + 32);   // [2 (block parity)][2 (column half)][128 rows]
+  float* xsum = xmax + 512;                            // [2 (column half)][128 rows]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -73,7 +76,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
     }
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(o_full, 1);
     mbar_fence_init();
   }
@@ -148,11 +151,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   } else {
     const int q = warp & 3;
     const int row = q * 32 + lane;           // row inside the query tile == TMEM lane
+    const int half = (warp - 2) >> 2;        // which 64 key columns / 64 output columns of the row this thread owns
+    const int c_begin = half * 2;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    float o[HD];
+    float o[HD / 2];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    for (int i = 0; i < HD / 2; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;    // l_run: this thread's half of the row sum
     const float sl2 = args.scale_log2;
     bool alive = true;
     for (int j = 0; j < n_kv && alive; ++j) {
@@ -165,7 +170,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const bool need_mask = (kv0 + BKV - 1 > limit);
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_begin; c < c_begin + 2; ++c) {
         uint32_t r[32];
         tmem_ld32(ts + c * 32, r);
         tmem_ld_wait();
@@ -178,13 +183,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
         }
       }
+      // combine with the partner thread's half (buffers alternate with the block parity: one barrier per block)
+      float* xm = xmax + (j & 1) * 256;
+      xm[half * 128 + row] = mx;
+      named_bar_sync(2, 256);
+      mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * sl2);
       const float neg_ms = -m_use * sl2;
       float rowsum = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_begin; c < c_begin + 2; ++c) {
         uint32_t r[32];
         tmem_ld32(ts + c * 32, r);
         tmem_ld_wait();
@@ -216,19 +226,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!mbar_wait(o_full, j & 1, 121)) { alive = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_O + lane_off + c * 32, r);
+        tmem_ld32(tmem_O + lane_off + (c_begin + c) * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int t = 0; t < 32; ++t) o[c * 32 + t] = fmaf(o[c * 32 + t], alpha, __uint_as_float(r[t]));
       }
     }
+    // total row sum = both halves
+    xsum[half * 128 + row] = l_run;
+    named_bar_sync(2, 256);
+    const float l_tot = l_run + xsum[(half ^ 1) * 128 + row];
     if (alive && q0 + row < args.S) {
-      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = args.out + ((long long)b * args.S + q0 + row) * args.out_stride + h * HD;
+      const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* dst = args.out + ((long long)b * args.S + q0 + row) * args.out_stride + h * HD + half * (HD / 2);
 #pragma unroll
-      for (int v = 0; v < HD / 8; ++v) {
+      for (int v = 0; v < HD / 16; ++v) {
         uint4 w;
         w.x = pack_bf16x2(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
         w.y = pack_bf16x2(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
@@ -236,8 +250,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         w.w = pack_bf16x2(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
         reinterpret_cast<uint4*>(dst)[v] = w;
       }
-      args.lse[((long long)b * args.Hq + h) * args.S + q0 + row] =
-          (l_run > 0.f) ? (m_run * args.scale + logf(l_run)) : -INFINITY;
+      if (half == 0)
+        args.lse[((long long)b * args.Hq + h) * args.S + q0 + row] = (l_tot > 0.f) ? (m_run * args.scale + logf(l_tot)) : -INFINITY;
     }
     tc_fence_before();
   }

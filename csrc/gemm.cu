@@ -66,6 +66,8 @@ struct FusedArgs {
   const void* peer_in[MAX_RANKS];
   uint8_t* layer_buf;
   long long shard_bytes, chunk_bytes, b_byte_off;
+  // optional: sum of squares of the (alpha-scaled) fp32 output, atomically added to *sumsq (gradient-norm fusion)
+  float* sumsq;
   // scatter
   int scatter;
   void* peer_grad[MAX_RANKS];
@@ -299,6 +301,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     bool alive = true;
     int lt = 0;
     uint32_t chunk_ctr = 0;
+    float ss = 0.f;  // sum of squares of this thread's outputs (rows / columns past the edges are exact zeros)
     for (int t = cta; t < num_tiles && alive; t += nctas, ++lt) {
       int m0, n0;
       tile_coords(t, m0, n0);
@@ -325,6 +328,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             o.y = alpha * __uint_as_float(r[4 * j + 1]);
             o.z = alpha * __uint_as_float(r[4 * j + 2]);
             o.w = alpha * __uint_as_float(r[4 * j + 3]);
+            ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
             *reinterpret_cast<float4*>(srow + ((j ^ (r_in_tile & 7)) << 4)) = o;
           }
         } else {
@@ -382,6 +386,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
     }
     if (store_thread && !fa.scatter) tma_store_wait0();
+    if (fa.sumsq != nullptr) {
+      ss = warp_sum(ss);
+      if (lane == 0) atomicAdd(fa.sumsq, ss);
+    }
   }
 
   tc_fence_before();
@@ -427,10 +435,23 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedA
 // fp32 (out_f32) with row pitch ldc.  Pitches are in elements and must be multiples of 8 (16-byte TMA
 // strides); base pointers must be 16-byte aligned.  sm_limit > 0 caps the persistent grid (leaves SMs
 // to a concurrent communication kernel).
+extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit,
+                                  float* sumsq, void* stream);
+
 extern "C" int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                             long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit,
                             void* stream) {
+  return yf_gemm_bf16_sumsq(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, alpha, sm_limit, nullptr, stream);
+}
+
+// Same as yf_gemm_bf16; when `sumsq` is given (fp32 output, no accumulation) the kernel also adds the sum of squares
+// of everything it wrote to *sumsq, so a gradient norm needs no extra pass over a freshly written weight gradient.
+extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit,
+                                  float* sumsq, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if (sumsq != nullptr && (!out_f32 || accumulate)) return -1;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
   GemmArgs args;
@@ -447,6 +468,7 @@ extern "C" int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
   FusedArgs fa;
   memset(&fa, 0, sizeof(fa));
+  fa.sumsq = sumsq;
   return use256 ? launch_gemm<256>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, fa, lda, ldb, sm_limit, s);
 }
 

@@ -61,3 +61,20 @@ def test_gemm_strided_views():
     ref = a.float() @ b.float().t()
     assert (c.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
     assert big_c[:, :256].abs().max().item() == 0 and big_c[:, 640:].abs().max().item() == 0
+
+
+def test_gemm_fused_sum_of_squares():
+    """The fp32 epilogue can add the squared norm of what it writes to a device scalar (gradient-norm fusion)."""
+    from yafsdp_b200.ops import kernels
+
+    torch.manual_seed(3)
+    m, n, k = 640, 1000, 256  # n not a multiple of the tile: clipped columns must not contribute
+    a = torch.randn(k, m, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    acc = torch.full((1,), 5.0, device="cuda")
+    kernels.gemm(a, b, a_mn_major=True, b_mn_major=True, out=out, sumsq=acc)
+    torch.cuda.synchronize()
+    kernels.check_status()
+    want = 5.0 + out.double().pow(2).sum().item()
+    assert abs(acc.item() - want) <= 1e-4 * want

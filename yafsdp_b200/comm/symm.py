@@ -124,8 +124,13 @@ class SymmBackend(CommBackend):
         self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
         # "ce": bulk peer transfers run on the copy engines (one cudaMemcpyAsync per peer) and only the reduction is a
         # kernel, so communication takes no SM from the GEMMs; "sm": the pull kernels do the transfers
-        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce").lower()
+        # Measured on B200 (Llama-2-7B step): with 2 ranks "ce" wins (124.5 vs 134.2 ms); with 8 ranks one copy stream
+        # moves ~200 GB/s per peer copy and the seven copies of a collective run back to back (168 ms), while the pull
+        # kernels read all peers at once (134.7 ms).  Hence the default below; the environment variable overrides it.
+        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce" if self.world == 2 else "sm").lower()
         self._staging: torch.Tensor | None = None
+        # copy-engine transfers from different peers go to several streams so that they run on different engines
+        self._ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(int(os.environ.get("YAFSDP_CE_STREAMS", "4")))]
         self.ag_ctas = int(os.environ.get("YAFSDP_AG_CTAS", "0"))
         self.rs_ctas = int(os.environ.get("YAFSDP_RS_CTAS", "0"))
         self._ptr_cache: dict[int, ctypes.Array] = {}
@@ -159,6 +164,34 @@ class SymmBackend(CommBackend):
     def step_barrier(self) -> None:
         self.barrier(0)
 
+    def _ce_copies(self, copies: list[tuple[int, int, int]]) -> None:
+        """``(dst, src, nbytes)`` device copies, ordered after the work already queued on the current stream and joined
+        back into it; spread over the copy streams when there are several."""
+        lib = _native.lib()
+        cur = torch.cuda.current_stream()
+        if len(self._ce_streams) <= 1 or len(copies) <= 1:
+            for d, s, n in copies:
+                rc = lib.yf_memcpy_async(d, s, n, cur.cuda_stream)
+                if rc != 0:
+                    raise RuntimeError(f"peer copy failed with code {rc}")
+        else:
+            start = torch.cuda.Event()
+            start.record(cur)
+            used: list[torch.cuda.Stream] = []
+            for i, (d, s, n) in enumerate(copies):
+                st = self._ce_streams[i % len(self._ce_streams)]
+                if st not in used:
+                    st.wait_event(start)
+                    used.append(st)
+                rc = lib.yf_memcpy_async(d, s, n, st.cuda_stream)
+                if rc != 0:
+                    raise RuntimeError(f"peer copy failed with code {rc}")
+            for st in used:
+                done = torch.cuda.Event()
+                done.record(st)
+                cur.wait_event(done)
+        kernels._launches += len(copies)
+
     # ------------------------------------------------------------------ collectives
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
         nbytes = inp.numel() * inp.element_size()
@@ -169,12 +202,7 @@ class SymmBackend(CommBackend):
             self._int_ptr_cache[inp.data_ptr()] = peers
             base = out.data_ptr()
             with torch.autograd._unsafe_preserve_version_counter(out):
-                for d in range(self.world):
-                    r = (self.rank + d) % self.world
-                    rc = lib.yf_memcpy_async(base + r * nbytes, peers[r], nbytes, stream)
-                    if rc != 0:
-                        raise RuntimeError(f"peer copy from rank {r} failed with code {rc}")
-            kernels._launches += self.world
+                self._ce_copies([(base + r * nbytes, peers[r], nbytes) for r in ((self.rank + d) % self.world for d in range(self.world))])
             return
         with torch.autograd._unsafe_preserve_version_counter(out):
             rc = _native.lib().yf_allgather_pull(self._peers(inp), out.data_ptr(), nbytes, self.rank, self.world, self.ag_ctas,
@@ -201,15 +229,14 @@ class SymmBackend(CommBackend):
             lib = _native.lib()
             sbase = self._staging.data_ptr()
             srcs = []
+            copies = []
             for r in range(self.world):
                 if r == self.rank:
                     srcs.append(inp.data_ptr())  # own chunk is read in place
                     continue
-                rc = lib.yf_memcpy_async(sbase + r * shard * esz, peers[r] + self.rank * shard * esz, shard * esz, stream)
-                if rc != 0:
-                    raise RuntimeError(f"peer copy from rank {r} failed with code {rc}")
+                copies.append((sbase + r * shard * esz, peers[r] + self.rank * shard * esz, shard * esz))
                 srcs.append(sbase + r * shard * esz - self.rank * shard * esz)  # the kernel adds rank * shard
-            kernels._launches += self.world - 1
+            self._ce_copies(copies)
             rc = lib.yf_reduce_scatter_pull(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
                                             int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas, stream)
         else:

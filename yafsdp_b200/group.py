@@ -147,9 +147,22 @@ class GradSink:
         self.index = index
         self.view = view
 
+    def norm_target(self, accumulate: bool) -> torch.Tensor | None:
+        """Where a kernel that writes this gradient once, completely and finally may add the sum of its squares (the
+        gradient norm then needs no pass of its own).  ``None`` when the value written is not final: another write will
+        accumulate into it, or a reduction over ranks follows."""
+        g = self.group
+        if g._norm_sq is None or not g._alias_grad:
+            return None
+        if accumulate:
+            g._norm_fused_ok = False
+            return None
+        return g._norm_sq
+
     def begin(self, zero: bool = False) -> tuple[torch.Tensor, bool]:
         g = self.group
         g._acquire_grad_buffer()
+        g._sink_counts[self.index] += 1
         accumulate = g._sink_written[self.index]
         if not accumulate and g._alias_grad:
             # single rank: the sink is the persistent sharded gradient itself, which may already hold
@@ -303,10 +316,14 @@ class ParamGroup:
         self._is_unsharded = False
         self._post_reduce_event: Any = None
         self._sink_written: list[bool] = [False] * len(self.params)
+        self._sink_counts: list[int] = [0] * len(self.params)
         self._holds_grad_buffer = False
         self._post_forward_indices: list[int] = []
         self._partial_reduce_pending = False
         self._kept_after_forward = False
+        # gradient-norm fusion (single rank): kernels that write a final gradient add its squared norm here
+        self._norm_sq: torch.Tensor | None = None
+        self._norm_fused_ok = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
 
@@ -509,8 +526,12 @@ class ParamGroup:
         with record_function(self._with_fqn("YaFSDP::pre_backward")):
             self._training_state = TrainingState.PRE_BACKWARD
             self._kept_after_forward = False
+            if self._norm_sq is not None and self._alias_grad and not self._has_sharded_grads():
+                self._norm_sq.zero_()
+                self._norm_fused_ok = True
             if not self._holds_grad_buffer:
                 self._sink_written = [False] * len(self.params)
+                self._sink_counts = [0] * len(self.params)
             if self.unshard_in_backward:
                 self.unshard(self.unshard_async_op)
                 self.wait_for_unshard()
@@ -585,6 +606,7 @@ class ParamGroup:
                     assert up is not None and sp.rs_view is not None
                     g = up.grad
                     if g is not None:
+                        self._norm_fused_ok = False
                         accumulate = self._sink_written[sp.index] or (self._alias_grad and not fresh and sp.sharded_param.grad is not None)  # type: ignore[union-attr]
                         (dsts_add if accumulate else dsts_copy).append((sp.rs_view, g))
                         up.grad = None
@@ -631,6 +653,7 @@ class ParamGroup:
         if self._alias_grad:
             # single rank, gradients already sit in the sharded gradient: at most a scale
             if scale != 1.0 or (pre or 1.0) != 1.0:
+                self._norm_fused_ok = False
                 with torch.no_grad():
                     self.sharded_grad_flat.mul_(scale / (pre or 1.0))
             self._finish_reduce(with_grad, None)
@@ -751,6 +774,11 @@ class ParamGroup:
         self.param_dtype, self.reduce_dtype = pd, rd
         self.all_gather_dtype = pd or self.orig_dtype
         self.reduce_scatter_dtype = rd or pd or self.orig_dtype
+
+    def _sink_written_twice(self, index: int) -> bool:
+        """True when the parameter's gradient already held a contribution before the latest sink write (so a kernel that
+        added into it did not produce the final value alone)."""
+        return self._sink_counts[index] > 1
 
     def _shares_nothing_data(self) -> bool:
         return self.world_size == 1

@@ -81,12 +81,13 @@ class _WeightGrad:
         if self.use_sinks:
             views, accs = zip(*[s.begin() for s in self.sinks])
             fused = fuse_adjacent(list(views)) if len(views) > 1 else views[0]
+            targets = [s.norm_target(acc) for s, acc in zip(self.sinks, accs)]
             if len(views) == 1 or (fused.data_ptr() == views[0].data_ptr() and len(set(accs)) == 1):
-                kernels.gemm(dy, x, a_mn_major=True, b_mn_major=True, out=fused, accumulate=accs[0])
+                kernels.gemm(dy, x, a_mn_major=True, b_mn_major=True, out=fused, accumulate=accs[0], sumsq=targets[0])
             else:
                 r0 = 0
-                for v, acc in zip(views, accs):
-                    kernels.gemm(dy[:, r0 : r0 + v.shape[0]], x, a_mn_major=True, b_mn_major=True, out=v, accumulate=acc)
+                for v, acc, tgt in zip(views, accs, targets):
+                    kernels.gemm(dy[:, r0 : r0 + v.shape[0]], x, a_mn_major=True, b_mn_major=True, out=v, accumulate=acc, sumsq=tgt)
                     r0 += v.shape[0]
             return [None] * len(self.params)
         dw = kernels.gemm(dy, x, a_mn_major=True, b_mn_major=True)
@@ -104,6 +105,9 @@ def _norm_weight_grad(w: torch.Tensor, fn: Any) -> torch.Tensor | None:
     if s is not None:
         view, _ = s.begin(zero=True)
         fn(view)
+        tgt = s.norm_target(s.group._sink_written_twice(s.index))
+        if tgt is not None:
+            kernels.sumsq_(view.reshape(-1), tgt)
         return None
     dw = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
     fn(dw)

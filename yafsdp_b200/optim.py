@@ -59,6 +59,11 @@ class ShardedAdamW:
         self.exp_avg_sq = [torch.zeros_like(g.master_flat, dtype=torch.float32) for g in self.groups]
         dev = self.groups[0].device
         self._norm_sq = torch.zeros(1, device=dev, dtype=torch.float32)
+        # one slot per group: weight-gradient kernels add the squared norm of what they write (single-rank fusion)
+        self._group_norm_sq = torch.zeros(len(self.groups), device=dev, dtype=torch.float32)
+        if max_grad_norm is not None and dev.type == "cuda":
+            for i, g in enumerate(self.groups):
+                g._norm_sq = self._group_norm_sq[i : i + 1]
         self._coef = torch.ones(1, device=dev, dtype=torch.float32)
         self.last_grad_norm = torch.zeros(1, device=dev, dtype=torch.float32)
 
@@ -82,12 +87,19 @@ class ShardedAdamW:
 
         dev = self._norm_sq.device
         self._norm_sq.zero_()
+        fused = []
         for i in active:
-            g = self.groups[i].sharded_grad_flat
+            grp = self.groups[i]
+            if grp._norm_sq is not None and grp._norm_fused_ok:
+                fused.append(i)  # the kernels that wrote the gradients already summed their squares
+                continue
+            g = grp.sharded_grad_flat
             if dev.type == "cuda":
                 kernels.sumsq_(g, self._norm_sq)
             else:
                 self._norm_sq += g.float().pow(2).sum()
+        if fused:
+            self._norm_sq += self._group_norm_sq[fused].sum() if len(fused) < len(self.groups) else self._group_norm_sq.sum()
         pg = self.groups[0].process_group
         if pg is not None and pg.size() > 1:
             dist.all_reduce(self._norm_sq, group=pg)

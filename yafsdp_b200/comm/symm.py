@@ -124,13 +124,13 @@ class SymmBackend(CommBackend):
         self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
         # "ce": bulk peer transfers run on the copy engines (one cudaMemcpyAsync per peer) and only the reduction is a
         # kernel, so communication takes no SM from the GEMMs; "sm": the pull kernels do the transfers
-        # Measured on B200 (Llama-2-7B step): with 2 ranks "ce" wins (124.5 vs 134.2 ms); with 8 ranks one copy stream
-        # moves ~200 GB/s per peer copy and the seven copies of a collective run back to back (168 ms), while the pull
-        # kernels read all peers at once (134.7 ms).  Hence the default below; the environment variable overrides it.
-        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce" if self.world == 2 else "sm").lower()
+        # Measured on B200 (Llama-2-7B step, ms): 2 ranks ce 124.5 / sm 134.2; 4 ranks ce (4 copy streams) 123.4 / sm 146.9;
+        # 8 ranks sm 134.7, ce with ONE copy stream 168 (one stream moves ~200 GB/s per peer copy and runs the seven
+        # copies of a collective back to back, hence one stream per peer below).
+        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce").lower()
         self._staging: torch.Tensor | None = None
         # copy-engine transfers from different peers go to several streams so that they run on different engines
-        self._ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(int(os.environ.get("YAFSDP_CE_STREAMS", "4")))]
+        self._ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(int(os.environ.get("YAFSDP_CE_STREAMS", str(max(1, min(self.world - 1, 8))))))]
         self.ag_ctas = int(os.environ.get("YAFSDP_AG_CTAS", "0"))
         self.rs_ctas = int(os.environ.get("YAFSDP_RS_CTAS", "0"))
         self._ptr_cache: dict[int, ctypes.Array] = {}

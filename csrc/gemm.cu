@@ -74,11 +74,6 @@ struct FusedArgs {
   long long c_flat_off, shard_numel;
 };
 
-YF_DEVINL uint4 ld_sys_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
 YF_DEVINL void st_release_gpu_u32(unsigned int* p, unsigned int v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -89,9 +84,30 @@ YF_DEVINL unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
 }
 YF_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
-// Communication role of the gather mode: chunk ids are (shard, chunk in shard); the chunks that cover B come
-// first (rotated by rank so that the ranks do not all read the same owner at the same time), then the rest.
-__device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes) {
+// Communication role of the gather mode.  One thread per communication CTA drives the TMA unit: bulk loads
+// (cp.async.bulk, no multicast) bring 16 KB pieces of a peer's shard into a ring in this CTA's shared memory and bulk
+// stores write them to the local layer buffer, several pieces in flight in both directions, so a handful of CTAs keep
+// NVLink busy without spending registers or issue slots on the copy.  Chunk ids are (shard, chunk in shard); the chunks
+// that cover B come first (rotated by rank so that the ranks do not all read the same owner at once), then the rest.
+constexpr int COMM_PIECE = 16384;
+constexpr int COMM_NBUF = 12;       // 192 KB ring
+constexpr int COMM_LOOKAHEAD = 6;   // loads issued this many pieces ahead of the stores
+
+YF_DEVINL void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+YF_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(gdst)),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
+__device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, uint8_t* ring, uint64_t* ring_bars) {
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&ring_bars[i], 1);
+  mbar_fence_init();
   const int cps = fa.chunks_per_shard;
   const int total = fa.world * cps;
   auto chunk_of = [&](long long byte_off) {
@@ -103,34 +119,72 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes) {
   const int last = chunk_of(fa.b_byte_off + b_bytes - 1);
   const int nprio = last - first + 1;
   const int rot = (int)(((long long)fa.rank * nprio) / fa.world);
-  for (int q = blockIdx.x; q < total; q += fa.n_comm) {
-    int id;
-    if (q < nprio) id = first + (q + rot) % nprio;
-    else id = (q - nprio < first) ? (q - nprio) : q;
+  auto chunk_id = [&](int q) {
+    if (q < nprio) return first + (q + rot) % nprio;
+    return (q - nprio < first) ? (q - nprio) : q;
+  };
+  // iterate pieces of this CTA's chunks through a two-cursor software pipeline: `ld` issues loads, `st` (COMM_LOOKAHEAD
+  // pieces behind) waits for a piece and stores it
+  struct Cursor {
+    int q;            // position in this CTA's chunk sequence
+    long long off;    // byte offset inside the chunk
+  };
+  Cursor ld{(int)blockIdx.x, 0}, st{(int)blockIdx.x, 0};
+  auto chunk_range = [&](int q, const uint8_t*& src, uint8_t*& dst, long long& bytes, int& id) {
+    id = chunk_id(q);
     const int r = id / cps, j = id - r * cps;
     const long long lo = (long long)j * fa.chunk_bytes;
     const long long hi = min(lo + fa.chunk_bytes, fa.shard_bytes);
-    if (hi > lo) {
-      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(fa.peer_in[r]) + lo);
-      uint4* dst = reinterpret_cast<uint4*>(fa.layer_buf + (long long)r * fa.shard_bytes + lo);
-      const long long nvec = (hi - lo) / 16;
-      long long i = threadIdx.x;
-      constexpr int CU = 16;  // 16-byte loads in flight per thread: 192 x 16 x 16 B = 48 KB per CTA
-      for (; i + (CU - 1) * GEMM_THREADS < nvec; i += CU * GEMM_THREADS) {
-        uint4 v[CU];
-#pragma unroll
-        for (int u = 0; u < CU; ++u) v[u] = ld_sys_v4(src + i + u * GEMM_THREADS);
-#pragma unroll
-        for (int u = 0; u < CU; ++u) dst[i + u * GEMM_THREADS] = v[u];
-      }
-      for (; i < nvec; i += GEMM_THREADS) dst[i] = ld_sys_v4(src + i);
+    bytes = hi > lo ? hi - lo : 0;
+    src = reinterpret_cast<const uint8_t*>(fa.peer_in[r]) + lo;
+    dst = fa.layer_buf + (long long)r * fa.shard_bytes + lo;
+  };
+  uint32_t n_ld = 0, n_st = 0;
+  bool alive = true;
+  while (alive && st.q < total) {
+    // ---- issue the next load (if any piece is left and the ring slot is free)
+    if (ld.q < total && n_ld < n_st + COMM_LOOKAHEAD) {
+      const uint8_t* src; uint8_t* dst; long long bytes; int id;
+      chunk_range(ld.q, src, dst, bytes, id);
+      if (bytes == 0) { ld.q += fa.n_comm; ld.off = 0; continue; }
+      const uint32_t piece = (uint32_t)min((long long)COMM_PIECE, bytes - ld.off);
+      const int slot = n_ld % COMM_NBUF;
+      // the store that last read this slot (piece n_ld - COMM_NBUF) must have finished reading shared memory; stores are
+      // committed in order, so at most COMM_NBUF - COMM_LOOKAHEAD - 1 younger ones may still be pending
+      if (n_ld >= COMM_NBUF) asm volatile("cp.async.bulk.wait_group.read 5;" ::: "memory");
+      mbar_expect_tx(&ring_bars[slot], piece);
+      bulk_load(ring + slot * COMM_PIECE, src + ld.off, piece, &ring_bars[slot]);
+      ++n_ld;
+      ld.off += piece;
+      if (ld.off >= bytes) { ld.q += fa.n_comm; ld.off = 0; }
+      continue;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    // ---- store the oldest loaded piece
+    const uint8_t* src; uint8_t* dst; long long bytes; int id;
+    chunk_range(st.q, src, dst, bytes, id);
+    if (bytes == 0) {
       __threadfence();
       st_release_gpu_u32(fa.flags + id, fa.epoch);
+      st.q += fa.n_comm; st.off = 0;
+      continue;
+    }
+    const uint32_t piece = (uint32_t)min((long long)COMM_PIECE, bytes - st.off);
+    const int slot = n_st % COMM_NBUF;
+    if (!mbar_wait(&ring_bars[slot], (n_st / COMM_NBUF) & 1, 12)) { alive = false; break; }
+    bulk_store(dst + st.off, ring + slot * COMM_PIECE, piece);
+    tma_store_commit();
+    ++n_st;
+    st.off += piece;
+    if (st.off >= bytes) {
+      // chunk complete: its bytes must be in global memory before the flag says so
+      tma_store_wait0();
+      fence_proxy_async_global();
+      __threadfence();
+      st_release_gpu_u32(fa.flags + id, fa.epoch);
+      st.q += fa.n_comm; st.off = 0;
     }
   }
+  tma_store_wait0();
 }
 
 template <int BLOCK_N>
@@ -139,7 +193,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
                          const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
   using Cfg = GemmCfg<BLOCK_N>;
   if (fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
-    gather_comm_role(fa, (long long)args.N * args.K * 2);
+    extern __shared__ uint8_t comm_smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 1023) & ~uintptr_t(1023));
+    gather_comm_role(fa, (long long)args.N * args.K * 2, ring, reinterpret_cast<uint64_t*>(ring + COMM_NBUF * COMM_PIECE));
     return;
   }
   const int cta = (int)blockIdx.x - fa.n_comm;        // index among the GEMM CTAs

@@ -63,6 +63,8 @@ class CommBackend:
     name = "abstract"
     #: True when gather inputs / reduce inputs must come from ``alloc`` (peer-mapped memory)
     needs_registered_buffers = False
+    #: True when all-gathers and reduce-scatters should share one communication stream
+    prefers_single_comm_stream = False
 
     def alloc(self, numel: int, dtype: torch.dtype, device: torch.device, kind: str) -> torch.Tensor:
         return torch.empty(numel, dtype=dtype, device=device)

@@ -124,10 +124,18 @@ class SymmBackend(CommBackend):
         self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
         # "ce": bulk peer transfers run on the copy engines (one cudaMemcpyAsync per peer) and only the reduction is a
         # kernel, so communication takes no SM from the GEMMs; "sm": the pull kernels do the transfers
-        # Measured on B200 (Llama-2-7B step, ms): 2 ranks ce 124.5 / sm 134.2; 4 ranks ce (4 copy streams) 123.4 / sm 146.9;
-        # 8 ranks sm 134.7, ce with ONE copy stream 168 (one stream moves ~200 GB/s per peer copy and runs the seven
-        # copies of a collective back to back, hence one stream per peer below).
-        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce").lower()
+        # Measured on B200 (Llama-2-7B step, ms): 2 ranks ce 124.5 / sm 134.2; 4 ranks ce (one copy stream per peer) 121.4 /
+        # sm 146.9; 8 ranks sm (one communication stream) 134.7 / ce with one copy stream 168 / ce with one stream per
+        # peer 142.2.  Hence the default: copy engines up to 4 ranks, pull kernels above.
+        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce" if self.world <= 4 else "sm").lower()
+        # the two collectives can use different transports: "ce" all-gather writes straight into the layer buffer and
+        # takes no SM; the reduction needs a kernel anyway, which can pull from the peers itself ("sm") or sum
+        # copy-engine-filled staging slots ("ce")
+        self.ag_transport = os.environ.get("YAFSDP_AG_TRANSPORT", self.transport).lower()
+        self.rs_transport = os.environ.get("YAFSDP_RS_TRANSPORT", self.transport).lower()
+        # pull kernels of the two collectives would compete for the same SM resources if they ran side by side: keep
+        # all-gathers and reduce-scatters on one stream then (copy-engine transfers do not have that problem)
+        self.prefers_single_comm_stream = self.rs_transport == "sm" and self.ag_transport == "sm"
         self._staging: torch.Tensor | None = None
         # copy-engine transfers from different peers go to several streams so that they run on different engines
         self._ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(int(os.environ.get("YAFSDP_CE_STREAMS", str(max(1, min(self.world - 1, 8))))))]
@@ -195,7 +203,7 @@ class SymmBackend(CommBackend):
     # ------------------------------------------------------------------ collectives
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
         nbytes = inp.numel() * inp.element_size()
-        if self.transport == "ce":
+        if self.ag_transport == "ce":
             lib = _native.lib()
             stream = torch.cuda.current_stream().cuda_stream
             peers = self.arena.peer_ptrs(inp) if inp.data_ptr() not in self._int_ptr_cache else self._int_ptr_cache[inp.data_ptr()]
@@ -216,7 +224,7 @@ class SymmBackend(CommBackend):
         shard = inp.numel() // self.world
         self.barrier(1)  # every rank's gradients for this group are complete
         stream = torch.cuda.current_stream().cuda_stream
-        if self.transport == "ce":
+        if self.rs_transport == "ce":
             # copy engines bring every peer's chunk for this rank into local staging slots; a local kernel sums them
             esz = inp.element_size()
             need = self.world * shard * esz

@@ -120,10 +120,13 @@ class CommContext:
 
     def lazy_init(self, device: torch.device, backend: CommBackend | None = None) -> None:
         self.streams = _DeviceStreams(device)
-        self.all_gather_stream = self.streams.new_stream(priority=-1)
-        self.reduce_scatter_stream = self.streams.new_stream(priority=-1)
         if backend is not None:
             self.backend = backend
+        self.all_gather_stream = self.streams.new_stream(priority=-1)
+        if self.backend.prefers_single_comm_stream:
+            self.reduce_scatter_stream = self.all_gather_stream
+        else:
+            self.reduce_scatter_stream = self.streams.new_stream(priority=-1)
 
     def get_all_gather_stream(self, async_op: bool, training_state: TrainingState) -> Any:
         assert self.streams is not None
@@ -405,7 +408,8 @@ class ParamGroup:
             view = data_flat[o : o + sp.numel].view(sp.orig_shape)
             sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad)
             sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape)
-            sp.sink = GradSink(self, sp.index, sp.rs_view) if sp.requires_grad else None
+            # kernels write fp32 gradients into the sink; with a 16-bit reduce dtype the autograd .grad path is used instead
+            sp.sink = GradSink(self, sp.index, sp.rs_view) if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 else None
             sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
         self._register_state_dict_hooks()
         self._lazy_inited = True

@@ -1,0 +1,53 @@
+"""Profiling / logging helpers (CPU)."""
+
+import io
+import json
+
+import torch
+
+
+def test_step_timer_and_logger():
+    from yafsdp_b200.utils.profiling import StepLogger, StepTimer
+
+    timer = StepTimer(torch.device("cpu"))
+    for _ in range(3):
+        with timer.step():
+            torch.randn(64, 64) @ torch.randn(64, 64)
+    s = timer.summary()
+    assert s["steps"] == 3 and s["host_ms_mean"] > 0
+    buf = io.StringIO()
+    log = StepLogger(tokens_per_step_per_gpu=2048, stream=buf)
+    rec = log.log(loss=3.5, iter_time_s=0.1, grad_norm=1.25)
+    assert rec["tokens_per_s_per_gpu"] == 20480.0 and log.step == 1
+    assert json.loads(buf.getvalue())["grad_norm"] == 1.25
+
+
+def test_profile_steps_writes_a_trace(tmp_path):
+    from yafsdp_b200.utils.profiling import profile_steps
+
+    path = tmp_path / "trace.json"
+    with profile_steps(str(path), wait=1, warmup=1, active=1) as prof:
+        for _ in range(4):
+            torch.randn(32, 32).sum()
+            prof.step()
+    assert path.exists() and "traceEvents" in json.loads(path.read_text())
+
+
+def test_checkpoint_module_recomputes():
+    from yafsdp_b200.utils.checkpointing import checkpoint_module
+
+    calls = []
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = torch.nn.Linear(4, 4)
+
+        def forward(self, x):
+            calls.append(1)
+            return torch.tanh(self.l(x))
+
+    m = checkpoint_module(M())
+    x = torch.randn(2, 4, requires_grad=True)
+    m(x).sum().backward()
+    assert len(calls) == 2 and m.l.weight.grad is not None  # forward ran again during backward

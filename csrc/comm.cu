@@ -36,9 +36,8 @@ YF_DEVINL unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
 
 // out[r * shard .. (r+1) * shard) = peer_r's shard, for every r.  Rank k starts with its own shard and
 // walks the peers in the order k+1, k+2, ...: at any moment every GPU reads from a different peer.
-constexpr int AG_UNROLL = 16;  // few warps, many loads in flight each: the kernel shares its SMs with the GEMM's six warps
-constexpr int AG_THREADS = 128;
-__global__ void __launch_bounds__(AG_THREADS) allgather_pull_kernel(PeerPtrs in, uint4* __restrict__ out, long long shard_vec, int rank, int world) {
+constexpr int AG_UNROLL = 4;
+__global__ void __launch_bounds__(512, 1) allgather_pull_kernel(PeerPtrs in, uint4* __restrict__ out, long long shard_vec, int rank, int world) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   for (int d = 0; d < world; ++d) {
@@ -61,10 +60,10 @@ __global__ void __launch_bounds__(AG_THREADS) allgather_pull_kernel(PeerPtrs in,
 // owner, in fp32, so the result is deterministic.  Wire format fp32 or bf16.  WORLD is a template parameter so
 // that the per-thread vectors stay in registers; each thread keeps about eight 16-byte peer loads in flight.
 template <bool BF16_WIRE, int WORLD>
-__global__ void __launch_bounds__(128) reduce_scatter_pull_kernel(PeerPtrs in, float* __restrict__ dst, long long shard_numel, int rank,
+__global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs in, float* __restrict__ dst, long long shard_numel, int rank,
                                                                   float scale, int accumulate) {
   constexpr int EPV = BF16_WIRE ? 8 : 4;  // elements per 16-byte vector on the wire
-  constexpr int U = (WORLD >= 16) ? 1 : (16 / WORLD);  // about sixteen 16-byte peer loads in flight per thread
+  constexpr int U = (WORLD >= 8) ? 1 : (8 / WORLD);
   const long long nvec = shard_numel / EPV;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const uint4* src[WORLD];
@@ -121,7 +120,7 @@ int launch_rs(PeerPtrs pp, float* dst, long long shard_numel, int rank, int worl
   switch (world) {
 #define YF_RS_CASE(W)                                                                                                        \
   case W:                                                                                                                    \
-    reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 128, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate);         \
+    reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 256, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate);         \
     return 0;
     YF_RS_CASE(1) YF_RS_CASE(2) YF_RS_CASE(3) YF_RS_CASE(4) YF_RS_CASE(5) YF_RS_CASE(6) YF_RS_CASE(7) YF_RS_CASE(8)
     YF_RS_CASE(16)
@@ -187,9 +186,9 @@ extern "C" int yf_allgather_pull(void* const* peer_in, void* out, long long shar
   if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
   for (int r = 0; r < world; ++r)
     if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
-  // one CTA of four warps per SM, next to the persistent GEMM CTA
+  // one CTA per SM: 512 threads x <= 64 registers leaves room for a persistent GEMM CTA on the same SM
   if (n_ctas <= 0) n_ctas = yf_num_sms();
-  allgather_pull_kernel<<<n_ctas, AG_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(peer_in, world), reinterpret_cast<uint4*>(out),
+  allgather_pull_kernel<<<n_ctas, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(peer_in, world), reinterpret_cast<uint4*>(out),
                                                                                    shard_bytes / 16, rank, world);
   return -(int)cudaGetLastError();
 }

@@ -73,10 +73,11 @@ class RaggedLoadPlanner(DefaultLoadPlanner):
                 raise RuntimeError(f"Missing key in checkpoint state_dict: {fqn}.")
             md = self.metadata.state_dict_metadata[fqn]
             if isinstance(obj, RaggedShardDTensor):
-                if not isinstance(md, TensorStorageMetadata) or len(md.size) != 1 or int(md.size[0]) != obj._spec.numel:
-                    raise ValueError(f"{fqn}: saved entry {getattr(md, 'size', None)} is not the flat form of a tensor with {obj._spec.numel} elements")
+                if not isinstance(md, TensorStorageMetadata) or len(md.size) != 1 or int(md.size[0]) != obj._spec.global_numel:
+                    raise ValueError(f"{fqn}: saved entry {getattr(md, 'size', None)} is not the flat form of a tensor with {obj._spec.global_numel} elements")
                 pl = obj._spec.placement
-                requests += _flat_read_items(fqn, md, pl.global_offset, pl.local_numel, (pl.global_offset,))
+                lo = obj._spec.outer_offset + pl.global_offset
+                requests += _flat_read_items(fqn, md, lo, pl.local_numel, (lo,))
             elif (isinstance(obj, torch.Tensor) and isinstance(md, TensorStorageMetadata) and len(md.size) == 1
                   and obj.dim() != 1 and int(md.size[0]) == obj.numel()):
                 if not obj.is_contiguous():

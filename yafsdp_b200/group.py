@@ -192,9 +192,15 @@ class ShardedParam:
     def __init__(self, info: ParamModuleInfo, param: nn.Parameter, index: int):
         self.info = info
         self.index = index
-        self.orig_shape = param.shape
+        # A parameter that already is a DTensor of an outer 1-D mesh (expert / tensor parallel, Shard(0)) is sharded
+        # further: this group flat-shards the piece that this rank holds on the outer mesh.
+        self.outer_mesh: Any = None
+        self.outer_placements: Any = None
+        self.outer_shape: torch.Size | None = None
+        inner = _outer_local(param, self)
+        self.orig_shape = inner.shape
         self.orig_dtype = param.dtype
-        self.numel = param.numel()
+        self.numel = inner.numel()
         self.requires_grad = param.requires_grad
         self.placement: ParamPlacement | None = None
         self.sharded_param: nn.Parameter | None = None
@@ -220,6 +226,22 @@ class ShardedParam:
         assert self.unsharded_param is not None
         self._set(self.unsharded_param)
         self.is_unsharded = True
+
+
+def _outer_local(param: torch.Tensor, sp: "ShardedParam | None" = None) -> torch.Tensor:
+    """The tensor to flat-shard: the parameter itself, or its local piece when it is a DTensor of an outer mesh."""
+    from torch.distributed.tensor import DTensor, Shard
+
+    if not isinstance(param, DTensor):
+        return param
+    mesh, placements = param.device_mesh, param.placements
+    if mesh.ndim != 1 or len(placements) != 1 or not (isinstance(placements[0], Shard) and placements[0].dim == 0):
+        raise NotImplementedError(f"fully_shard composes with parameters sharded as Shard(0) on a 1-D mesh, got {placements} on {mesh}")
+    if param.shape[0] % mesh.size() != 0:
+        raise NotImplementedError("the outer Shard(0) dimension must divide evenly over the outer mesh")
+    if sp is not None:
+        sp.outer_mesh, sp.outer_placements, sp.outer_shape = mesh, placements, param.shape
+    return param._local_tensor
 
 
 def _get_param_module_infos(params: list[nn.Parameter], modules: tuple[nn.Module, ...]) -> list[ParamModuleInfo]:
@@ -272,7 +294,7 @@ class ParamGroup:
         self._init_mp_dtypes(params)
 
         # ---- flat layout and persistent shards
-        self.layout = FlatLayout([p.numel() for p in params], self.world_size, shard_alignment)
+        self.layout = FlatLayout([sp.numel for sp in self.params], self.world_size, shard_alignment)
         self._master = torch.zeros(self.layout.shard_numel, dtype=self.orig_dtype, device=device)
         self._sharded_grad_flat: torch.Tensor | None = None
         mesh = mesh_info.mesh
@@ -282,11 +304,11 @@ class ParamGroup:
                 sp.placement = pl
                 local = self._master[pl.shard_offset : pl.shard_offset + pl.local_numel]
                 if pl.local_numel and p.device.type != "meta":
-                    src = p.detach().reshape(-1)[pl.global_offset : pl.global_offset + pl.local_numel]
+                    src = _outer_local(p.detach()).reshape(-1)[pl.global_offset : pl.global_offset + pl.local_numel]
                     local.copy_(src)
                 spec = RaggedSpec(
                     mesh, (RaggedShard(pl.local_numel, pl.global_offset, pl.shard_numels),), torch.Size(sp.orig_shape),
-                    _contiguous_stride(sp.orig_shape), self.orig_dtype,
+                    _contiguous_stride(sp.orig_shape), self.orig_dtype, sp.outer_mesh, sp.outer_placements, sp.outer_shape,
                 )
                 sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
                 for attr in ("_yf_init_fn",):
@@ -406,10 +428,16 @@ class ParamGroup:
         for sp in self.params:
             o = self.layout.flat_offsets[sp.index]
             view = data_flat[o : o + sp.numel].view(sp.orig_shape)
+            if sp.outer_mesh is not None:
+                from torch.distributed.tensor import DTensor
+
+                view = DTensor.from_local(view, sp.outer_mesh, sp.outer_placements, run_check=False, shape=sp.outer_shape,
+                                          stride=_contiguous_stride(sp.outer_shape))
             sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad)
             sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape)
             # kernels write fp32 gradients into the sink; with a 16-bit reduce dtype the autograd .grad path is used instead
-            sp.sink = GradSink(self, sp.index, sp.rs_view) if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 else None
+            sp.sink = (GradSink(self, sp.index, sp.rs_view)
+                       if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 and sp.outer_mesh is None else None)
             sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
         self._register_state_dict_hooks()
         self._lazy_inited = True
@@ -609,6 +637,11 @@ class ParamGroup:
                     up = sp.unsharded_param
                     assert up is not None and sp.rs_view is not None
                     g = up.grad
+                    if g is not None and sp.outer_mesh is not None:
+                        # gradient of a DTensor parameter: bring it to the parameter's own placement, take the local piece
+                        if tuple(g.placements) != tuple(sp.outer_placements):
+                            g = g.redistribute(placements=sp.outer_placements)
+                        g = g._local_tensor
                     if g is not None:
                         self._norm_fused_ok = False
                         accumulate = self._sink_written[sp.index] or (self._alias_grad and not fresh and sp.sharded_param.grad is not None)  # type: ignore[union-attr]

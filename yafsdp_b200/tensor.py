@@ -57,6 +57,11 @@ class RaggedSpec:
     shape: torch.Size
     stride: tuple[int, ...]
     dtype: torch.dtype
+    # set when the logical tensor is itself the local piece of a DTensor sharded as Shard(0) over an outer 1-D mesh
+    # (expert / tensor parallelism composed with this sharding)
+    outer_mesh: DeviceMesh | None = None
+    outer_placements: tuple | None = None
+    outer_shape: torch.Size | None = None
 
     @property
     def tensor_meta(self) -> SimpleNamespace:
@@ -74,7 +79,21 @@ class RaggedSpec:
         return n
 
     def with_dtype(self, dtype: torch.dtype) -> "RaggedSpec":
-        return self if dtype == self.dtype else RaggedSpec(self.mesh, self.placements, self.shape, self.stride, dtype)
+        if dtype == self.dtype:
+            return self
+        return RaggedSpec(self.mesh, self.placements, self.shape, self.stride, dtype, self.outer_mesh, self.outer_placements,
+                          self.outer_shape)
+
+    @property
+    def outer_offset(self) -> int:
+        """Flat offset of this rank's outer piece inside the full (outer-unsharded) tensor."""
+        if self.outer_mesh is None:
+            return 0
+        return self.outer_mesh.get_local_rank() * self.numel
+
+    @property
+    def global_numel(self) -> int:
+        return self.numel * (self.outer_mesh.size() if self.outer_mesh is not None else 1)
 
     def group(self) -> dist.ProcessGroup | None:
         return None if self.mesh is None else self.mesh.get_group(0)
@@ -218,7 +237,7 @@ class RaggedShardDTensor(torch.Tensor):
         world = len(pl.shard_numels)
         local = self._local_tensor.detach()
         if world == 1 or spec.mesh is None:
-            return local.reshape(spec.shape).clone()
+            return self._outer_full(local.reshape(spec.shape).clone())
         group = spec.group()
         width = max(max(pl.shard_numels), 1)
         send = local.new_zeros(width)
@@ -226,7 +245,15 @@ class RaggedShardDTensor(torch.Tensor):
         recv = local.new_empty(world * width)
         dist.all_gather_into_tensor(recv, send, group=group)
         pieces = [recv[r * width : r * width + n] for r, n in enumerate(pl.shard_numels) if n > 0]
-        return torch.cat(pieces).reshape(spec.shape)
+        return self._outer_full(torch.cat(pieces).reshape(spec.shape))
+
+    def _outer_full(self, inner: torch.Tensor) -> torch.Tensor:
+        spec = self._spec
+        if spec.outer_mesh is None:
+            return inner
+        from torch.distributed.tensor import DTensor
+
+        return DTensor.from_local(inner, spec.outer_mesh, spec.outer_placements, run_check=False).full_tensor()
 
     # ---------------------------------------------------------------- dispatch
     @classmethod
@@ -287,7 +314,7 @@ class RaggedShardDTensor(torch.Tensor):
         from torch.distributed.checkpoint.metadata import ChunkStorageMetadata
 
         pl = self._spec.placement
-        return ChunkStorageMetadata(offsets=torch.Size([pl.global_offset]), sizes=torch.Size([pl.local_numel]))
+        return ChunkStorageMetadata(offsets=torch.Size([self._spec.outer_offset + pl.global_offset]), sizes=torch.Size([pl.local_numel]))
 
     def __create_write_items__(self, fqn: str, obj: Any) -> list[Any]:
         from torch.distributed.checkpoint.metadata import MetadataIndex, TensorProperties
@@ -301,7 +328,7 @@ class RaggedShardDTensor(torch.Tensor):
                 tensor_data=TensorWriteData(
                     chunk=chunk,
                     properties=TensorProperties.create_from_tensor(self._local_tensor),
-                    size=torch.Size([self._spec.numel]),
+                    size=torch.Size([self._spec.global_numel]),
                 ),
             )
         ]
@@ -311,7 +338,7 @@ class RaggedShardDTensor(torch.Tensor):
 
     def __get_tensor_shard__(self, index: Any) -> torch.Tensor:
         pl = self._spec.placement
-        if index.offset is not None and tuple(index.offset) != (pl.global_offset,):
+        if index.offset is not None and tuple(index.offset) != (self._spec.outer_offset + pl.global_offset,):
             raise ValueError(f"no shard at offset {tuple(index.offset)} for {index.fqn}: this rank holds offset {pl.global_offset}")
         return self._local_tensor
 

@@ -106,8 +106,10 @@ def max_over_ranks(x: float, device: torch.device) -> float:
     return float(t.item())
 
 
-def timed_steps(step_fn, batches, k: int, device: torch.device) -> float:
-    """Milliseconds for exactly k calls of step_fn, CUDA events on the launching stream, barrier + sync on both sides."""
+def timed_steps(step_fn, batches, k: int, device: torch.device, finish=None) -> float:
+    """Milliseconds for exactly k calls of step_fn, CUDA events on the launching stream, barrier + sync on both sides.
+    ``finish`` joins work that the steps left on side streams (an optimizer overlapped with the next forward) into the
+    launching stream before the closing event, so the timed region contains all of the k steps' work."""
     dist.barrier()
     torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
@@ -115,6 +117,8 @@ def timed_steps(step_fn, batches, k: int, device: torch.device) -> float:
     start.record()
     for i in range(k):
         step_fn(batches[i % len(batches)])
+    if finish is not None:
+        finish()
     end.record()
     torch.cuda.synchronize()
     dist.barrier()
@@ -125,6 +129,7 @@ def run(args, make_step) -> dict:
     rank, world, device = setup_dist(args.gpus)
     cfg_name, seq, batch = args.model, args.seq_len, args.batch
     step_dev, step_e2e, vocab, launch_counter, extra = make_step(args, rank, world, device)
+    finish = extra.pop("_finish", None)
     gen = torch.Generator().manual_seed(1 + rank)
     n_batches = 4
     host_batches = [torch.randint(0, vocab, (batch, seq), generator=gen).pin_memory() for _ in range(n_batches)]
@@ -136,10 +141,10 @@ def run(args, make_step) -> dict:
     if rank == 0:
         sampler.start()
     l0 = launch_counter()
-    ms = timed_steps(step_dev, dev_batches, args.steps, device)
+    ms = timed_steps(step_dev, dev_batches, args.steps, device, finish)
     launches = launch_counter() - l0
     step_e2e(host_batches[0])  # one untimed pass through the end-to-end path
-    ms_e2e = timed_steps(step_e2e, host_batches, args.steps, device)
+    ms_e2e = timed_steps(step_e2e, host_batches, args.steps, device, finish)
     clocks = sampler.stop() if rank == 0 else {}
     tokens = batch * seq * world * args.steps
     value = tokens / (ms / 1e3)
@@ -207,7 +212,8 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
         return step(ids_host).item()
 
     backend = args.comm_backend if args.comm_backend != "auto" else ("symm" if world > 1 else "none (single rank: buffers aliased)")
-    return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, {"comm_backend": backend, "params": cfg.num_params()}
+    return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, {
+        "comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join}
 
 
 # ----------------------------------------------------------------------------------------- reference

@@ -575,7 +575,7 @@ extern "C" int yf_embedding_bwd(const void* dout, const long long* ids, float* d
   YF_LAUNCH_RET();
 }
 extern "C" int yf_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, const float* grad_scale_ptr, long long n,
-                        float lr, float beta1, float beta2, float eps, float weight_decay, int step, void* stream) {
+                        float lr, float beta1, float beta2, float eps, float weight_decay, int step, int max_ctas, void* stream) {
   if (n <= 0) return 0;
   if (!aligned16(p) || !aligned16(g) || !aligned16(m) || !aligned16(v) || (p_bf16 && (reinterpret_cast<uintptr_t>(p_bf16) & 7)))
     return -1;
@@ -583,7 +583,11 @@ extern "C" int yf_adamw(float* p, const float* g, float* m, float* v, void* p_bf
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
   a.bc1 = 1.f - powf(beta1, (float)step);
   a.bc2 = 1.f - powf(beta2, (float)step);
-  adamw_kernel<<<grid_for(n / 4 + 1, 256, 8), 256, 0, YF_STREAM(stream)>>>(p, g, m, v, (__nv_bfloat16*)p_bf16, grad_scale_ptr, n, a);
+  // max_ctas > 0 caps the grid: when the update runs beside GEMMs on another stream, three CTAs per SM leave the
+  // thread slots and registers that a persistent GEMM CTA needs and still keep HBM saturated
+  int grid = grid_for(n / 4 + 1, 256, 8);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  adamw_kernel<<<grid, 256, 0, YF_STREAM(stream)>>>(p, g, m, v, (__nv_bfloat16*)p_bf16, grad_scale_ptr, n, a);
   YF_LAUNCH_RET();
 }
 extern "C" int yf_sumsq(const float* g, long long n, float* out, void* stream) {

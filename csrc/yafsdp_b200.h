@@ -40,7 +40,7 @@ int yf_cross_entropy(void* logits, const long long* labels, float* loss_rows, in
 int yf_embedding_fwd(const void* table, const long long* ids, void* out, long long T, int D, int V, void* stream);
 int yf_embedding_bwd(const void* dout, const long long* ids, float* dtable, long long T, int D, int V, void* stream);
 int yf_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, const float* grad_scale_ptr, long long n,
-             float lr, float beta1, float beta2, float eps, float weight_decay, int step, void* stream);
+             float lr, float beta1, float beta2, float eps, float weight_decay, int step, int max_ctas, void* stream);
 int yf_sumsq(const float* g, long long n, float* out, void* stream);
 int yf_clip_coef(const float* total_sq, float max_norm, float* coef, float* norm_out, void* stream);
 int yf_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);

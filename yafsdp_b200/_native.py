@@ -145,7 +145,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_cross_entropy": [_P, _P, _P, _I, _I, _L, _F, _I, _P],
         "yf_embedding_fwd": [_P, _P, _P, _L, _I, _I, _P],
         "yf_embedding_bwd": [_P, _P, _P, _L, _I, _I, _P],
-        "yf_adamw": [_P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _P],
+        "yf_adamw": [_P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _I, _P],
         "yf_sumsq": [_P, _L, _P, _P],
         "yf_clip_coef": [_P, _F, _P, _P, _P],
         "yf_cast_f32_to_bf16": [_P, _P, _L, _P],

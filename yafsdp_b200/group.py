@@ -346,6 +346,7 @@ class ParamGroup:
         self._post_forward_indices: list[int] = []
         self._partial_reduce_pending = False
         self._kept_after_forward = False
+        self._optim_event: Any = None
         # gradient-norm fusion (single rank): kernels that write a final gradient add its squared norm here
         self._norm_sq: torch.Tensor | None = None
         self._norm_fused_ok = False
@@ -460,6 +461,17 @@ class ParamGroup:
         self._ag_input_version = self._master._version
         self._ag_input_fresh = True
 
+    def wait_optimizer(self) -> None:
+        """An optimizer that updates this group on a side stream (overlapped with the next forward) leaves an event here;
+        whoever reads the parameters next on the current stream waits for it first."""
+        ev = self._optim_event
+        if ev is not None:
+            self._optim_event = None
+            if self.comm_ctx is not None and self.comm_ctx.streams is not None:
+                self.comm_ctx.streams.wait_event(None, ev)
+            elif self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).wait_event(ev)
+
     def mark_gather_input_fresh(self) -> None:
         """The fused optimizer kernel wrote the compute-dtype copy itself."""
         self._ag_input_version = self._master._version
@@ -476,6 +488,7 @@ class ParamGroup:
         logger.debug("unshard %s", self._module_fqn)
         with record_function(self._with_fqn("YaFSDP::all_gather")):
             if self._alias_data:
+                self.wait_optimizer()
                 self._refresh_gather_input()
                 self._ag_event = None
                 self._unshard_pending = True
@@ -762,6 +775,7 @@ class ParamGroup:
         self._sd_hooks = handles
 
     def _to_sharded_for_state_dict(self) -> None:
+        self.wait_optimizer()
         if self._is_unsharded or self._unshard_pending:
             self.reshard()
 

@@ -206,11 +206,12 @@ def embedding_bwd_(dout: torch.Tensor, ids: torch.Tensor, dtable_f32: torch.Tens
 
 def adamw_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, p_bf16: torch.Tensor | None,
            grad_scale: torch.Tensor | None, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
-           step: int) -> None:
+           step: int, max_ctas: int = 0) -> None:
     n = p.numel()
     assert p.dtype == g.dtype == m.dtype == v.dtype == torch.float32
     _check(_native.lib().yf_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _ptr(p_bf16), _ptr(grad_scale), n,
-                                  float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step), _stream()),
+                                  float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step), int(max_ctas),
+                                  _stream()),
            "yf_adamw")
 
 

@@ -142,6 +142,7 @@ def main() -> None:
             print(json.dumps({"step": i, "loss": round(loss, 4), "iter_time_s": round(dt, 4),
                               "tokens_per_s_per_gpu": round(args.batch * args.seq_len / dt, 1),
                               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2) if device.type == "cuda" else None}))
+    opt.join()
     if dist.is_initialized():
         dist.destroy_process_group()
 

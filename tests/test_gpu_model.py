@@ -135,3 +135,53 @@ def test_optimizer_overlap_matches_plain_stepping():
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def _single_rank_group():
+    import os
+    import torch.distributed as dist
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29581")
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=0, world_size=1)
+        return True
+    return False
+
+
+def test_micro_batch_accumulation_and_checkpointing_on_gpu():
+    """Two micro-batches accumulated through the gradient sinks (TMA reduce-add epilogue) equal one batch of both; the
+    same with activation checkpointing on every layer (recompute inside backward)."""
+    import torch.distributed as dist
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.optim import param_groups_of
+    from yafsdp_b200.train import build_llama
+
+    created = _single_rank_group()
+    try:
+        dev = torch.device("cuda", 0)
+        cfg = CONFIGS["tiny-gpu"]
+        ids = torch.randint(0, cfg.vocab_size, (4, 256), device=dev)
+
+        def grads(model, batches):
+            for g in param_groups_of(model):
+                for sp in g.params:
+                    sp.sharded_param.grad = None
+            for b in batches:
+                (model(b, labels=b) / len(batches)).backward()
+            return [g.sharded_grad_flat.clone() for g in param_groups_of(model)]
+
+        base = build_llama(cfg, dev, seed=1)
+        whole = grads(base, [ids])
+        halves = grads(base, [ids[:2], ids[2:]])
+        ckpt = build_llama(cfg, dev, seed=1, checkpoint_layers=cfg.num_hidden_layers)
+        whole_ckpt = grads(ckpt, [ids])
+        for a, b, c in zip(whole, halves, whole_ckpt):
+            scale = a.abs().max().item() + 1e-6
+            assert (a - b).abs().max().item() <= 3e-2 * scale, "accumulated micro-batches differ from the full batch"
+            assert (a - c).abs().max().item() <= 3e-2 * scale, "activation checkpointing changed the gradients"
+        from yafsdp_b200.ops import kernels
+        kernels.check_status()
+    finally:
+        if created:
+            dist.destroy_process_group()

@@ -4,7 +4,7 @@
 // system-scope relaxed loads (never through L1).  The kernels use no shared memory and few registers, so
 // their CTAs co-reside on the SMs with the persistent tcgen05 GEMM CTAs instead of taking SMs away.
 //
-// Every wait on another GPU is bounded: when the budget runs out the kernel records
+// Every wait on another GPU is bounded: when the time limit runs out the kernel records
 // YF_ERR_FLAG_TIMEOUT in the status word and returns.
 #include <string.h>
 

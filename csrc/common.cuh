@@ -41,7 +41,7 @@ void yf_register_status(yf_status_fn fn);
     YfStatusReg() { yf_register_status(&yf_tu_status); }                      \
   } yf_status_reg_instance;
 
-// default wait budget in nanoseconds (2 s); peers/flags use their own, shorter ones
+// default wait limit in nanoseconds (2 s); waits on peers and flags pass their own limit
 #define YF_WAIT_NS_DEFAULT 2000000000ull
 
 YF_DEVINL uint64_t yf_globaltimer() {

@@ -21,8 +21,6 @@ Gradient divide factors follow ``ya_fsdp/_collectives.py:221-267``.
 
 from __future__ import annotations
 
-from typing import Any
-
 import torch
 import torch.distributed as dist
 

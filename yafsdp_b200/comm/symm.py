@@ -161,6 +161,14 @@ class SymmBackend(CommBackend):
             self._ptr_cache[key] = arr
         return arr
 
+    def _peer_ints(self, t: torch.Tensor) -> list[int]:
+        key = t.data_ptr()
+        ptrs = self._int_ptr_cache.get(key)
+        if ptrs is None:
+            ptrs = self.arena.peer_ptrs(t)
+            self._int_ptr_cache[key] = ptrs
+        return ptrs
+
     # ------------------------------------------------------------------ ordering between GPUs
     def barrier(self, slot: int = 0) -> None:
         """All ranks' current streams meet here (device-side, bounded wait)."""
@@ -206,8 +214,7 @@ class SymmBackend(CommBackend):
         if self.ag_transport == "ce":
             lib = _native.lib()
             stream = torch.cuda.current_stream().cuda_stream
-            peers = self.arena.peer_ptrs(inp) if inp.data_ptr() not in self._int_ptr_cache else self._int_ptr_cache[inp.data_ptr()]
-            self._int_ptr_cache[inp.data_ptr()] = peers
+            peers = self._peer_ints(inp)
             base = out.data_ptr()
             with torch.autograd._unsafe_preserve_version_counter(out):
                 self._ce_copies([(base + r * nbytes, peers[r], nbytes) for r in ((self.rank + d) % self.world for d in range(self.world))])
@@ -230,10 +237,7 @@ class SymmBackend(CommBackend):
             need = self.world * shard * esz
             if self._staging is None or self._staging.numel() < need:
                 self._staging = torch.empty(need, dtype=torch.uint8, device=self.device)
-            peers = self._int_ptr_cache.get(inp.data_ptr())
-            if peers is None:
-                peers = self.arena.peer_ptrs(inp)
-                self._int_ptr_cache[inp.data_ptr()] = peers
+            peers = self._peer_ints(inp)
             lib = _native.lib()
             sbase = self._staging.data_ptr()
             srcs = []

@@ -132,8 +132,8 @@ class YaFSDP(nn.Module):
         module.set_comm_backend(comm_backend, num_grad_buffers=2 if zero_stage >= 2 else None)  # type: ignore[attr-defined]
         if zero_stage <= 1:
             module._get_fsdp_state()._lazy_init(allow_no_grad_reduce=True)  # type: ignore[attr-defined]
-        if gradient_accumulation_steps > 1 or True:
-            module.set_gradient_divide_factor(float(self._dp_size * gradient_accumulation_steps))  # type: ignore[attr-defined]
+        # reduced gradients are divided by dp_size * accumulation steps, so the flat gradients hold the mean after the last micro-batch
+        module.set_gradient_divide_factor(float(self._dp_size * gradient_accumulation_steps))  # type: ignore[attr-defined]
         self._flat_params: list[nn.Parameter] | None = None
 
     # ------------------------------------------------------------------ module protocol

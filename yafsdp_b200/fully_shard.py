@@ -15,7 +15,7 @@ import torch.nn as nn
 from torch.distributed.device_mesh import DeviceMesh, init_device_mesh
 
 from .api import MixedPrecisionPolicy
-from .common import ShardMeshInfo, TrainingState
+from .common import ShardMeshInfo
 from .group import ParamGroup
 from .state import FSDPState, get_module_state
 

@@ -644,7 +644,7 @@ class ParamGroup:
                 return
             self._acquire_grad_buffer()
             fresh = self._alias_grad and not self._has_sharded_grads()
-            srcs, dsts_copy, dsts_add = [], [], []
+            dsts_copy, dsts_add = [], []
             with torch.no_grad():
                 for sp in self.params:
                     up = sp.unsharded_param
@@ -670,7 +670,6 @@ class ParamGroup:
                     torch._foreach_copy_([d for d, _ in dsts_copy], [s for _, s in dsts_copy])
                 if dsts_add:
                     torch._foreach_add_([d for d, _ in dsts_add], [s.to(d.dtype) if s.dtype != d.dtype else s for d, s in dsts_add])
-            del srcs
         if not self.reduce_grads:
             with record_function(self._with_fqn("YaFSDP::post_backward_reshard")):
                 if self.reshard_after_backward:

@@ -15,7 +15,7 @@ Flow of one step (``ya_fsdp/_state.py:39-678`` is the reference for the behaviou
 from __future__ import annotations
 
 import functools
-from typing import Any, Callable
+from typing import Any
 
 import torch
 import torch.nn as nn

@@ -1,0 +1,73 @@
+"""All-gather tensor extensions: a parameter class that travels as int8 (quantised shard + scale metadata) and is
+dequantised after the gather."""
+
+import pytest
+import torch
+import torch.nn as nn
+
+from dist_utils import run_distributed
+
+SCALE = 1.0 / 64
+
+
+class Int8Weight(torch.Tensor):
+    """Plain-storage tensor subclass: fp32 master values, gathered as int8 with a fixed scale."""
+
+    calls = {"pre": 0, "post": 0}
+
+    def fsdp_pre_all_gather(self, mesh):
+        Int8Weight.calls["pre"] += 1
+        q = torch.clamp(torch.round(self.as_subclass(torch.Tensor) / SCALE), -127, 127).to(torch.int8)
+        return (q,), {"scale": SCALE}
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype, *, out=None):
+        Int8Weight.calls["post"] += 1
+        (q,) = all_gather_outputs
+        deq = q.to(param_dtype) * metadata["scale"]
+        if out is not None:
+            out.copy_(deq)
+            return None
+        return deq, (q,)
+
+
+def _worker(rank, world):
+    from yafsdp_b200 import MixedPrecisionPolicy, RaggedShardDTensor, fully_shard
+
+    torch.manual_seed(0)
+    lin = nn.Linear(24, 16, bias=False)
+    full = lin.weight.detach().clone()
+    lin.weight = nn.Parameter(lin.weight.data.as_subclass(Int8Weight))
+    norm = nn.LayerNorm(24)
+    model = nn.Sequential(norm, lin)
+    policy = MixedPrecisionPolicy(all_gather_dtype_to_param_cls={torch.int8: Int8Weight})
+    fully_shard(lin, mp_policy=policy)
+    fully_shard(norm)
+    fully_shard(model)
+    g = lin._get_fsdp_state()._param_group
+    assert g.all_gather_dtype == torch.int8 and isinstance(lin.weight, RaggedShardDTensor)
+    x = torch.randn(4, 24, generator=torch.Generator().manual_seed(5 + rank))
+    out = model(x)
+    want_w = torch.clamp(torch.round(full / SCALE), -127, 127) * SCALE  # every rank computes with the dequantised weight
+    ref = nn.functional.linear(nn.functional.layer_norm(x, (24,)), want_w)
+    assert torch.allclose(out, ref, atol=1e-5)
+    assert g.gather_input.dtype == torch.int8 and g.gather_input.numel() == g.layout.shard_numel
+    out.sum().backward()
+    assert isinstance(lin.weight.grad, RaggedShardDTensor) and lin.weight.grad.dtype == torch.float32
+    # the master stays fp32 and trainable; a second step re-quantises the updated shard and refreshes in place
+    with torch.no_grad():
+        lin.weight._local_tensor.add_(0.5)
+    pre, post = Int8Weight.calls["pre"], Int8Weight.calls["post"]
+    out2 = model(x)
+    assert Int8Weight.calls["pre"] == pre + 1 and Int8Weight.calls["post"] > post, (pre, post, Int8Weight.calls, g._is_unsharded, type(lin.weight))
+    want_w2 = torch.clamp(torch.round((full + 0.5) / SCALE), -127, 127) * SCALE
+    assert torch.allclose(out2, nn.functional.linear(nn.functional.layer_norm(x, (24,)), want_w2), atol=1e-5)
+    # mixing extension and ordinary parameters in one group is refused with a clear message
+    lin2 = nn.Linear(8, 8)
+    lin2.weight = nn.Parameter(lin2.weight.data.as_subclass(Int8Weight))
+    with pytest.raises(AssertionError, match="group of their own"):
+        fully_shard(lin2, mp_policy=policy)
+
+
+@pytest.mark.timeout(120)
+def test_all_gather_extension_int8():
+    run_distributed(_worker, 2)

@@ -305,3 +305,30 @@ def _v1_worker(rank, world):
 @pytest.mark.timeout(180)
 def test_v1_class_wrapper():
     run_distributed(_v1_worker, 2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _mp_refresh_worker(rank, world):
+    """Mixed precision with a stock torch optimizer: the bf16 gather input follows the fp32 master after every step."""
+    from yafsdp_b200 import MixedPrecisionPolicy
+
+    pol = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, cast_forward_inputs=True)
+    model = _shard(_build(), mp_policy=pol)
+    opt = torch.optim.AdamW(model.parameters(), lr=5e-2, foreach=True)
+    losses = []
+    for _ in range(4):
+        opt.zero_grad()
+        loss = _loss(model, _data(rank))
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+        for m in [model.emb, *model.layers]:
+            g = m._get_fsdp_state()._param_group
+            g.unshard(); g.wait_for_unshard(); g.reshard()  # a gather right after the step must see the new weights
+            assert torch.equal(g.gather_input, g.master_flat.to(torch.bfloat16)), "stale compute-dtype copy after optimizer step"
+    assert losses[-1] < losses[0]
+
+
+@pytest.mark.timeout(120)
+def test_mixed_precision_gather_input_follows_torch_optimizer():
+    run_distributed(_mp_refresh_worker, 2)

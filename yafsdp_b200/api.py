@@ -19,8 +19,9 @@ class MixedPrecisionPolicy:
     ``output_dtype``: cast floating-point forward outputs to this dtype.
     ``cast_forward_inputs``: cast floating-point forward inputs to ``param_dtype`` (default off).
     ``bit32_acc_for_bit16_reduce_scatter``: bf16 on the wire, fp32 accumulation (needs ``reduce_dtype=bf16``).
-    ``all_gather_dtype_to_param_cls``: all-gather dtype -> tuple of parameter classes gathered in that dtype
-    through the ``fsdp_pre_all_gather`` / ``fsdp_post_all_gather`` tensor-extension hooks.
+    ``all_gather_dtype_to_param_cls``: all-gather dtype -> parameter tensor class (or tuple of classes) gathered in
+    that dtype through the ``fsdp_pre_all_gather`` / ``fsdp_post_all_gather`` tensor-extension hooks (fp8-style
+    parameters).  A group gathers in one dtype: such parameters go into ``fully_shard`` groups of their own.
     """
 
     param_dtype: torch.dtype | None = None

@@ -202,11 +202,21 @@ class ShardedParam:
         self.orig_dtype = param.dtype
         self.numel = inner.numel()
         self.requires_grad = param.requires_grad
+        # all-gather extension (``fsdp_pre_all_gather`` / ``fsdp_post_all_gather`` defined by the parameter's tensor class):
+        # the local shard is presented to the hooks as an instance of that class
+        data = param.data
+        has_pre, has_post = hasattr(data, "fsdp_pre_all_gather"), hasattr(data, "fsdp_post_all_gather")
+        if has_pre != has_post:
+            raise AssertionError(f"Both fsdp_pre_all_gather and fsdp_post_all_gather should be defined if using all-gather extensions: {type(data)}")
+        self.ext_cls: type | None = type(data) if has_pre else None
+        self.ext_local: torch.Tensor | None = None
+        self.ext_metadata: Any = None
         self.placement: ParamPlacement | None = None
         self.sharded_param: nn.Parameter | None = None
         self.sharded_grad: RaggedShardDTensor | None = None
         self.unsharded_param: nn.Parameter | None = None
         self.rs_view: torch.Tensor | None = None
+        self.gathered_view: torch.Tensor | None = None
         self.sink: GradSink | None = None
         self.is_unsharded = False
         self.fqn: str | None = None
@@ -311,6 +321,8 @@ class ParamGroup:
                     _contiguous_stride(sp.orig_shape), self.orig_dtype, sp.outer_mesh, sp.outer_placements, sp.outer_shape,
                 )
                 sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
+                if sp.ext_cls is not None:
+                    sp.ext_local = local.as_subclass(sp.ext_cls)
                 for attr in ("_yf_init_fn",):
                     if hasattr(p, attr):
                         setattr(sp.sharded_param, attr, getattr(p, attr))
@@ -346,6 +358,7 @@ class ParamGroup:
         self._post_forward_indices: list[int] = []
         self._partial_reduce_pending = False
         self._kept_after_forward = False
+        self._has_extensions = False
         self._optim_event: Any = None
         # gradient-norm fusion (single rank): kernels that write a final gradient add its squared norm here
         self._norm_sq: torch.Tensor | None = None
@@ -368,6 +381,18 @@ class ParamGroup:
         self.reduce_dtype = rd
         self.all_gather_dtype = pd or self.orig_dtype
         self.reduce_scatter_dtype = rd or pd or self.orig_dtype
+        # parameter classes that are gathered in their own dtype through the tensor-extension hooks; one all-gather dtype
+        # per group, so a group holds either only such parameters (of one dtype) or none
+        mapping = self.mp_policy.all_gather_dtype_to_param_cls
+        if mapping:
+            for dtype, classes in mapping.items():
+                classes = classes if isinstance(classes, tuple) else (classes,)
+                hits = [isinstance(p.data, classes) for p in params]
+                if all(hits):
+                    self.all_gather_dtype = dtype
+                elif any(hits):
+                    raise AssertionError(
+                        f"a fully_shard group gathers in one dtype: put the {classes} parameters (gathered as {dtype}) in a group of their own")
 
     # ------------------------------------------------------------------ sizes
     @property
@@ -410,7 +435,8 @@ class ParamGroup:
         self.grad_ctx = grad_ctx
         backend = comm_ctx.backend
         single = self.world_size == 1
-        need_cast = self.all_gather_dtype != self.orig_dtype
+        self._has_extensions = any(sp.ext_cls is not None for sp in self.params)
+        need_cast = self.all_gather_dtype != self.orig_dtype or self._has_extensions
         # all-gather input
         if need_cast or backend.needs_registered_buffers:
             self._ag_input = backend.alloc(self.layout.shard_numel, self.all_gather_dtype, self.device, "gather_input")
@@ -434,12 +460,16 @@ class ParamGroup:
 
                 view = DTensor.from_local(view, sp.outer_mesh, sp.outer_placements, run_check=False, shape=sp.outer_shape,
                                           stride=_contiguous_stride(sp.outer_shape))
-            sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad)
+            sp.gathered_view = view
+            # extension parameters get their unsharded tensor from fsdp_post_all_gather at the first unshard
+            sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad) if sp.ext_cls is None else None
             sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape)
             # kernels write fp32 gradients into the sink; with a 16-bit reduce dtype the autograd .grad path is used instead
             sp.sink = (GradSink(self, sp.index, sp.rs_view)
-                       if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 and sp.outer_mesh is None else None)
-            sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
+                       if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 and sp.outer_mesh is None
+                       and sp.ext_cls is None else None)
+            if sp.unsharded_param is not None:
+                sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
         self._register_state_dict_hooks()
         self._lazy_inited = True
 
@@ -452,7 +482,22 @@ class ParamGroup:
         if self._ag_input_fresh and self._ag_input_version == self._master._version:
             return
         with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(self._ag_input):
-            if self._master.is_cuda and self.orig_dtype == torch.float32 and self.all_gather_dtype == torch.bfloat16:
+            if self._has_extensions:
+                for sp in self.params:
+                    pl = sp.placement
+                    assert pl is not None
+                    dst = self._ag_input[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                    if sp.ext_cls is not None:
+                        assert sp.ext_local is not None
+                        (src,), sp.ext_metadata = sp.ext_local.fsdp_pre_all_gather(self.mesh_info.mesh)
+                        if src.dtype != self.all_gather_dtype or src.numel() != pl.local_numel:
+                            raise AssertionError(
+                                f"fsdp_pre_all_gather must return one tensor of dtype {self.all_gather_dtype} with the local shard's "
+                                f"{pl.local_numel} elements, got {src.dtype} with {src.numel()}")
+                        dst.copy_(src.reshape(-1))
+                    else:
+                        dst.copy_(self._master[pl.shard_offset : pl.shard_offset + pl.local_numel])
+            elif self._master.is_cuda and self.orig_dtype == torch.float32 and self.all_gather_dtype == torch.bfloat16:
                 from .ops import kernels
 
                 kernels.cast_f32_to_bf16_(self._master, self._ag_input)
@@ -519,10 +564,28 @@ class ParamGroup:
         assert self.comm_ctx is not None and self.comm_ctx.streams is not None
         self.comm_ctx.streams.wait_event(None, self._ag_event)
         self._ag_event = None
+        if self._has_extensions:
+            self._run_post_all_gather_hooks()
         for sp in self.params:
             sp.to_unsharded()
         self._unshard_pending = False
         self._is_unsharded = True
+
+    def _run_post_all_gather_hooks(self) -> None:
+        """Extension parameters: the hook turns the gathered data into the tensor the module computes with; the first call
+        creates it, later calls refresh it in place (``out=``)."""
+        compute_dtype = self.param_dtype or self.orig_dtype
+        with torch.no_grad():
+            for sp in self.params:
+                if sp.ext_cls is None:
+                    continue
+                assert sp.ext_local is not None
+                if sp.unsharded_param is None:
+                    unsharded, _ = sp.ext_local.fsdp_post_all_gather((sp.gathered_view,), sp.ext_metadata, compute_dtype)
+                    sp.unsharded_param = nn.Parameter(unsharded, requires_grad=sp.requires_grad)
+                    sp.unsharded_param._yf_grad_sink = None  # type: ignore[attr-defined]
+                else:
+                    sp.ext_local.fsdp_post_all_gather((sp.gathered_view,), sp.ext_metadata, compute_dtype, out=sp.unsharded_param.data)
 
     def reshard(self) -> None:
         if self._unshard_pending:
@@ -762,6 +825,9 @@ class ParamGroup:
             if self.reshard_after_backward:
                 self.reshard()
         self._post_forward_indices.clear()
+        # an optimizer step normally follows: the compute-dtype copy is re-derived at the next gather unless the fused
+        # optimizer writes it itself (it then marks it fresh again)
+        self._ag_input_fresh = False
 
     # ------------------------------------------------------------------ state dict
     def _register_state_dict_hooks(self) -> None:

@@ -165,6 +165,8 @@ class ShardedAdamW:
                            weight_decay=self.weight_decay, step=self.step_count, max_ctas=max_ctas)
             if bf16_out is not None:
                 g.mark_gather_input_fresh()
+            else:
+                g._ag_input_fresh = False  # the kernel updated the master behind autograd's version counter
         else:
             gr = grad.float() * (coef if coef is not None else 1.0)
             pf = p.float()

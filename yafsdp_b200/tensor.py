@@ -266,7 +266,10 @@ class RaggedShardDTensor(torch.Tensor):
         spec = proto._spec
 
         if func in (aten.detach.default, aten.alias.default):
-            return RaggedShardDTensor(func(args[0]._local_tensor), spec, requires_grad=False)
+            # the new outer tensor keeps the SAME inner tensor: a detach issued at this dispatch level would alias the
+            # storage but start a fresh autograd version counter, and in-place optimizer updates on a parameter must stay
+            # visible (through the counter) on the flat master shard the inner tensor is a view of
+            return RaggedShardDTensor(args[0]._local_tensor, spec, requires_grad=False)
         if func in _NORM_OPS:
             return _norm_op(func, args, kwargs, spec)
         if func in _RANDOM_INPLACE:

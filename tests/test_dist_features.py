@@ -332,3 +332,38 @@ def _mp_refresh_worker(rank, world):
 @pytest.mark.timeout(120)
 def test_mixed_precision_gather_input_follows_torch_optimizer():
     run_distributed(_mp_refresh_worker, 2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _prefetch_api_worker(rank, world):
+    """Explicit prefetch lists, post-optimizer event, divide factor, forced-sum reduction: same numbers as the defaults."""
+    model = _shard(_build())
+    layers = list(model.layers)
+    for i, l in enumerate(layers[:-1]):
+        l.set_modules_to_forward_prefetch([layers[i + 1]])
+    for i, l in enumerate(layers[1:], start=1):
+        l.set_modules_to_backward_prefetch([layers[i - 1]])
+    with pytest.raises(ValueError):
+        layers[0].set_modules_to_forward_prefetch([nn.Linear(2, 2)])
+    model.set_force_sum_reduction_for_comms(True)
+    model.set_post_optim_event(None)
+    model.set_is_last_backward(True)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-2)
+    for _ in range(2):
+        opt.zero_grad()
+        _loss(model, _data(rank * 10)).backward()
+        opt.step()
+    _check_params(model, _reference_params(world, 2, 1))
+    # a custom divide factor rescales the reduced gradient
+    model2 = _shard(_build())
+    model2.set_gradient_divide_factor(float(world * 4))
+    _loss(model2, _data(rank * 10)).backward()
+    ref = _build()
+    for r in range(world):
+        (_loss(ref, _data(r * 10)) / (world * 4)).backward()
+    assert torch.allclose(model2.layers[0].a.weight.grad.full_tensor(), ref.layers[0].a.weight.grad, atol=1e-6)
+
+
+@pytest.mark.timeout(180)
+def test_prefetch_lists_and_reduction_knobs():
+    run_distributed(_prefetch_api_worker, 2)

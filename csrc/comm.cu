@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(512, 1) allgather_pull_kernel(PeerPtrs in, uin
 // that the per-thread vectors stay in registers; each thread keeps about eight 16-byte peer loads in flight.
 template <bool BF16_WIRE, int WORLD>
 __global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs in, float* __restrict__ dst, long long shard_numel, int rank,
-                                                                  float scale, int accumulate) {
+                                                                  float scale, int accumulate, float* __restrict__ sumsq) {
+  float ss = 0.f;  // squared norm of what this thread writes (gradient-norm fusion, optional)
   constexpr int EPV = BF16_WIRE ? 8 : 4;  // elements per 16-byte vector on the wire
   constexpr int U = (WORLD >= 8) ? 1 : (8 / WORLD);
   const long long nvec = shard_numel / EPV;
@@ -108,19 +109,24 @@ __global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs in, f
           const float4 old = d4[h];
           o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
         }
+        ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
         d4[h] = o;
       }
     }
+  }
+  if (sumsq != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) atomicAdd(sumsq, ss);
   }
 }
 
 template <bool BF16_WIRE>
 int launch_rs(PeerPtrs pp, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate, int n_ctas,
-              cudaStream_t st) {
+              float* sumsq, cudaStream_t st) {
   switch (world) {
 #define YF_RS_CASE(W)                                                                                                        \
   case W:                                                                                                                    \
-    reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 256, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate);         \
+    reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 256, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate, sumsq);  \
     return 0;
     YF_RS_CASE(1) YF_RS_CASE(2) YF_RS_CASE(3) YF_RS_CASE(4) YF_RS_CASE(5) YF_RS_CASE(6) YF_RS_CASE(7) YF_RS_CASE(8)
     YF_RS_CASE(16)
@@ -193,8 +199,17 @@ extern "C" int yf_allgather_pull(void* const* peer_in, void* out, long long shar
   return -(int)cudaGetLastError();
 }
 
+extern "C" int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
+                                            int accumulate, int bf16_wire, int n_ctas, float* sumsq, void* stream);
+
 extern "C" int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
                                       int accumulate, int bf16_wire, int n_ctas, void* stream) {
+  return yf_reduce_scatter_pull_sumsq(peer_in, dst, shard_numel, rank, world, scale, accumulate, bf16_wire, n_ctas, nullptr, stream);
+}
+
+// Same; when `sumsq` is given the kernel also adds the squared norm of the values it leaves in dst to *sumsq.
+extern "C" int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
+                                            int accumulate, int bf16_wire, int n_ctas, float* sumsq, void* stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || shard_numel <= 0 || (shard_numel % 8)) return -1;
   if (reinterpret_cast<uintptr_t>(dst) & 15) return -1;
   for (int r = 0; r < world; ++r)
@@ -202,8 +217,8 @@ extern "C" int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long lon
   if (n_ctas <= 0) n_ctas = yf_num_sms();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const PeerPtrs pp = to_peers(peer_in, world);
-  const int rc = bf16_wire ? launch_rs<true>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, st)
-                           : launch_rs<false>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, st);
+  const int rc = bf16_wire ? launch_rs<true>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, sumsq, st)
+                           : launch_rs<false>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, sumsq, st);
   if (rc != 0) return rc;
   return -(int)cudaGetLastError();
 }

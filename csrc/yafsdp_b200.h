@@ -70,6 +70,8 @@ int yf_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void*
 int yf_allgather_pull(void* const* peer_in, void* out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
 int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
                            int accumulate, int bf16_wire, int n_ctas, void* stream);
+int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
+                                 int accumulate, int bf16_wire, int n_ctas, float* sumsq, void* stream);
 int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream);
 int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream);
 int yf_flag_set(void* flags, long long index, long long value, void* stream);

@@ -89,6 +89,12 @@ def _collectives_worker(rank, world):
             be.reduce_scatter(dst, g, dist.group.WORLD, scale=1.0 / world, accumulate=True)
             torch.cuda.synchronize()
             assert torch.allclose(dst, 1 + want / world, rtol=1e-5, atol=1e-5)
+            # gradient-norm fusion: the kernel also sums the squares of what it leaves in dst
+            ss = torch.zeros(1, device=dev, dtype=torch.float32)
+            assert be.reduce_scatter(dst, g, dist.group.WORLD, scale=1.0 / world, accumulate=False, sumsq=ss)
+            torch.cuda.synchronize()
+            assert torch.allclose(dst, want / world, rtol=1e-5, atol=1e-5)
+            assert torch.allclose(ss, dst.double().pow(2).sum().float(), rtol=1e-4)
     kernels.check_status()
 
 

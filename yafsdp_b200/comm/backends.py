@@ -79,7 +79,9 @@ class CommBackend:
         scale: float,
         accumulate: bool,
         acc_fp32: bool = True,
-    ) -> None:
+        sumsq: torch.Tensor | None = None,
+    ) -> bool:
+        """Returns True when ``sumsq`` was given and the squared norm of the final ``dst`` values was added to it."""
         raise NotImplementedError
 
     def step_barrier(self) -> None:
@@ -114,7 +116,8 @@ class TorchBackend(CommBackend):
         scale: float,
         accumulate: bool,
         acc_fp32: bool = True,
-    ) -> None:
+        sumsq: torch.Tensor | None = None,
+    ) -> bool:
         world = 1 if group is None else group.size()
         shard = inp.numel() // world
         rank = 0 if group is None else group.rank()
@@ -132,6 +135,7 @@ class TorchBackend(CommBackend):
             dst.add_(own)
         elif dst.data_ptr() != own.data_ptr():
             dst.copy_(own)
+        return False
 
 
 def make_backend(name: str | None, device: torch.device, group: dist.ProcessGroup | None) -> CommBackend:

@@ -225,7 +225,7 @@ class SymmBackend(CommBackend):
         kernels._check(rc, "yf_allgather_pull")
 
     def reduce_scatter(self, dst: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None, *, scale: float,
-                       accumulate: bool, acc_fp32: bool = True) -> None:
+                       accumulate: bool, acc_fp32: bool = True, sumsq: torch.Tensor | None = None) -> bool:
         if dst.dtype != torch.float32 or inp.dtype not in (torch.float32, torch.bfloat16):
             raise NotImplementedError("the symmetric reduce-scatter produces fp32 from an fp32 or bf16 wire format")
         shard = inp.numel() // self.world
@@ -249,13 +249,16 @@ class SymmBackend(CommBackend):
                 copies.append((sbase + r * shard * esz, peers[r] + self.rank * shard * esz, shard * esz))
                 srcs.append(sbase + r * shard * esz - self.rank * shard * esz)  # the kernel adds rank * shard
             self._ce_copies(copies)
-            rc = lib.yf_reduce_scatter_pull(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                            int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas, stream)
+            rc = lib.yf_reduce_scatter_pull_sumsq(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                  int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
+                                                  None if sumsq is None else sumsq.data_ptr(), stream)
         else:
-            rc = _native.lib().yf_reduce_scatter_pull(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                                      int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas, stream)
+            rc = _native.lib().yf_reduce_scatter_pull_sumsq(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                            int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
+                                                            None if sumsq is None else sumsq.data_ptr(), stream)
         kernels._check(rc, "yf_reduce_scatter_pull")
         self.barrier(2)  # every owner has read this rank's buffer: it may be overwritten
+        return sumsq is not None
 
     def check(self) -> None:
         kernels.check_status()

@@ -781,12 +781,19 @@ class ParamGroup:
                 self._grad_flat.div_(pre)
             dst = self.sharded_grad_flat
             if all_fresh or all_have:
-                self.comm_ctx.backend.reduce_scatter(
+                # the reduction kernel can also sum the squares of the final shard (gradient-norm fusion) when this is the
+                # only contribution of the step to the sharded gradient
+                target = self._norm_sq if (self._norm_sq is not None and all_fresh and dst.dtype == torch.float32) else None
+                if target is not None:
+                    target.zero_()
+                fused = self.comm_ctx.backend.reduce_scatter(
                     dst, self._grad_flat, self.process_group, scale=scale, accumulate=all_have and not all_fresh,
-                    acc_fp32=True,
+                    acc_fp32=True, sumsq=target,
                 )
+                self._norm_fused_ok = bool(fused)
             else:
                 # mixed: some parameters accumulate, some start fresh -> reduce into the own chunk, then per parameter
+                self._norm_fused_ok = False
                 own = self._grad_flat[self.rank * self.layout.shard_numel : (self.rank + 1) * self.layout.shard_numel]
                 self.comm_ctx.backend.reduce_scatter(own, self._grad_flat, self.process_group, scale=scale, accumulate=False)
                 for sp in with_grad:

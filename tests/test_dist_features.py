@@ -367,3 +367,47 @@ def _prefetch_api_worker(rank, world):
 @pytest.mark.timeout(180)
 def test_prefetch_lists_and_reduction_knobs():
     run_distributed(_prefetch_api_worker, 2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _hpz_worker(rank, world):
+    """Hierarchical partitioning: the first layers gather their weights for backward inside a 2-rank group."""
+    import torch.distributed as dist
+    from yafsdp_b200.comm import backends
+    from yafsdp_b200.compat_v1 import YaFSDP
+
+    intra = None
+    for lo in range(0, world, 2):
+        g = dist.new_group([lo, lo + 1])
+        if rank // 2 == lo // 2:
+            intra = g
+    sizes = []
+    orig = backends.TorchBackend.all_gather
+
+    def spy(self, out, inp, group):
+        sizes.append(1 if group is None else group.size())
+        return orig(self, out, inp, group)
+
+    backends.TorchBackend.all_gather = spy
+    model = _build()
+    wrapped = YaFSDP(
+        model, zero_stage=3, param_dtype=torch.float32,
+        modules_to_wrap_with_names=[(l, f"layers.{i}") for i, l in enumerate(model.layers)] + [(model.emb, "emb"), (model.head, "head")],
+        gradient_accumulation_steps=1, rogue_layer_norm_modules_with_names={model.norm: "norm"}, comm_backend="torch",
+        hpz_first_layers_num=2, intra_node_data_parallel_process_group=intra,
+    )
+    opt = torch.optim.SGD(list(wrapped.parameters()), lr=1e-2)
+    for step in range(2):
+        sizes.clear()
+        wrapped.zero_grad()
+        _loss(wrapped, _data(rank * 10)).backward()
+        opt.step()
+        # forward: 6 gathers over the whole group; backward: layers 0 and 1 inside the pair, the last-used groups stay gathered
+        assert sizes.count(2) == 2, sizes
+        assert sizes.count(world) >= 6, sizes
+    _check_params(model, _reference_params(world, 2, 1))
+
+
+@pytest.mark.timeout(240)
+def test_hierarchical_partitioning_secondary_shards():
+    run_distributed(_hpz_worker, 4)

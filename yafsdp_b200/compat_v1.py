@@ -20,8 +20,8 @@ The class maps the old arguments onto the same core that ``fully_shard`` uses:
 
 Not carried over: the closed-source communication library switches (``use_yccl*``: accepted and ignored with
 a warning; the peer-memory backend plays that role, ``comm_backend="symm"``), ``yccl_intra_inter_expr`` (an
-``eval`` of a user string) and hierarchical partitioning across nodes (``hpz_first_layers_num``: a single
-NVSwitch box has no slower inter-node tier; accepted, must be 0).
+``eval`` of a user string).  ``hpz_first_layers_num`` keeps a secondary shard of the first layers' weights inside
+``intra_node_data_parallel_process_group`` (default: one group per node) and gathers them for backward from there.
 """
 
 from __future__ import annotations
@@ -71,8 +71,8 @@ class YaFSDP(nn.Module):
         comm_backend: str = "auto",
     ):
         super().__init__()
-        if hpz_first_layers_num:
-            raise ValueError("hpz_first_layers_num > 0 is not supported: one NVSwitch box has no secondary (intra-node) shard tier")
+        if hpz_first_layers_num and zero_stage < 3:
+            raise ValueError("hpz_first_layers_num needs zero_stage=3: with weights kept gathered there is no backward all-gather")
         if use_yccl or yccl_intra_inter_expr is not None or yccl_all_gather_stages is not None:
             warnings.warn("the closed-source communication library options are ignored; use comm_backend='symm'", stacklevel=2)
         if model_parallel_process_group is not None and model_parallel_process_group.size() > 1:
@@ -129,6 +129,10 @@ class YaFSDP(nn.Module):
         if leftover:
             warnings.warn(f"{len(leftover)} parameters are outside the wrapped modules; they are sharded with the root group", stacklevel=2)
         fully_shard(module, **kw)
+        if hpz_first_layers_num:
+            intra = intra_node_data_parallel_process_group or _intra_node_group(pg, device_type)
+            for sub in wrapped[:hpz_first_layers_num]:
+                sub.set_secondary_shard_group(intra)  # type: ignore[attr-defined]
         module.set_comm_backend(comm_backend, num_grad_buffers=2 if zero_stage >= 2 else None)  # type: ignore[attr-defined]
         if zero_stage <= 1:
             module._get_fsdp_state()._lazy_init(allow_no_grad_reduce=True)  # type: ignore[attr-defined]
@@ -197,6 +201,21 @@ class YaFSDP(nn.Module):
 
     def load_state_dict(self, state_dict: dict[str, Any], *args: Any, **kwargs: Any) -> None:  # type: ignore[override]
         _ckpt.load_local_state_dict_v1(self.module, state_dict)
+
+
+def _intra_node_group(pg: dist.ProcessGroup, device_type: str) -> dist.ProcessGroup | None:
+    """Groups of consecutive ranks, one per node (``ya_fsdp/ya_fsdp.py:180-184``); every rank creates every group."""
+    per_node = torch.cuda.device_count() if device_type == "cuda" else 1
+    world = pg.size()
+    if per_node <= 1 or per_node >= world or world % per_node:
+        return None
+    ranks = dist.get_process_group_ranks(pg)
+    mine = None
+    for lo in range(0, world, per_node):
+        g = dist.new_group(ranks[lo : lo + per_node])
+        if pg.rank() // per_node == lo // per_node:
+            mine = g
+    return mine
 
 
 def _broadcast_module(module: nn.Module, group: dist.ProcessGroup) -> None:

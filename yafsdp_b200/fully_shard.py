@@ -284,6 +284,13 @@ class YaFSDPModule:
             if s._param_group is not None:
                 s._param_group.force_sum_reduction_for_comms = enable
 
+    def set_secondary_shard_group(self, group: Any, *, recurse: bool = False) -> None:
+        """Hierarchical partitioning for this module's parameter group: gather the weights for backward inside ``group``
+        (e.g. the ranks of one node) from a secondary shard saved after the forward all-gather."""
+        for state in self._states(recurse):
+            if state._param_group is not None:
+                state._param_group.set_secondary_shard_group(group)
+
     def set_comm_backend(self, name: str, *, num_grad_buffers: int | None = None) -> None:
         """Root only, before the first forward: ``"torch"`` (NCCL / gloo), ``"symm"`` (peer-memory kernels)
         or ``"auto"``; optionally the number of rotating gradient buffers."""

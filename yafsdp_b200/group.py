@@ -29,6 +29,7 @@ import contextlib
 from typing import Any, Callable, Iterator, NamedTuple
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 from torch.profiler import record_function
 
@@ -365,6 +366,42 @@ class ParamGroup:
         self._norm_fused_ok = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
+        # hierarchical partitioning: a secondary shard of the gathered weights kept inside a smaller (intra-node) group
+        self.secondary_group: dist.ProcessGroup | None = None
+        self._secondary_shard: torch.Tensor | None = None
+        self._secondary_valid = False
+        self._secondary_backend: CommBackend | None = None
+
+    # ------------------------------------------------------------------ hierarchical partitioning
+    def set_secondary_shard_group(self, group: dist.ProcessGroup | None) -> None:
+        """Keep, after each forward all-gather, this rank's ``1 / group.size()`` piece of the gathered weights, and gather
+        the weights for backward inside ``group`` only (ZeRO++-style hierarchical partitioning; the reference's
+        ``hpz_first_layers_num``, ``ya_fsdp/ya_fsdp.py:832-838,925-935,1015-1021``).  ``group`` must hold consecutive
+        ranks of the shard group, the same number on every rank."""
+        if group is not None:
+            n = group.size()
+            if self.world_size % n != 0:
+                raise ValueError(f"the secondary group's size {n} must divide the shard group's size {self.world_size}")
+            if n == self.world_size or self.world_size == 1:
+                group = None  # the primary shards already are what a group of that size would keep
+        self.secondary_group = group
+        self._secondary_shard = None
+        self._secondary_valid = False
+
+    def _secondary_chunk(self) -> torch.Tensor:
+        assert self.secondary_group is not None
+        n = self.secondary_group.size()
+        chunk = self.layout.padded_numel // n
+        r = self.secondary_group.rank()
+        return self._data_flat[r * chunk : (r + 1) * chunk]
+
+    def _save_secondary_shard(self) -> None:
+        chunk = self._secondary_chunk()
+        if self._secondary_shard is None:
+            self._secondary_shard = torch.empty_like(chunk)
+            self._secondary_backend = TorchBackend()
+        self._secondary_shard.copy_(chunk)
+        self._secondary_valid = True
 
     # ------------------------------------------------------------------ dtypes
     def _init_mp_dtypes(self, params: list[nn.Parameter]) -> None:
@@ -521,6 +558,7 @@ class ParamGroup:
         """The fused optimizer kernel wrote the compute-dtype copy itself."""
         self._ag_input_version = self._master._version
         self._ag_input_fresh = True
+        self._secondary_valid = False
 
     # ------------------------------------------------------------------ unshard / reshard
     def unshard(self, async_op: bool = False) -> None:
@@ -552,9 +590,17 @@ class ParamGroup:
                     st.wait_stream(stream, st.current())
             st.wait_event(stream, ctx.release_event)
             with st.use(stream):
-                self._refresh_gather_input()
-                assert self._ag_input is not None
-                cc.backend.all_gather(self._data_flat, self._ag_input, self.process_group)
+                if (self.secondary_group is not None and self._secondary_valid
+                        and (self._training_state != TrainingState.FORWARD or is_backward_running())):
+                    # backward of a hierarchically partitioned group: the weights come from the secondary shards
+                    assert self._secondary_shard is not None and self._secondary_backend is not None
+                    self._secondary_backend.all_gather(self._data_flat, self._secondary_shard, self.secondary_group)
+                    self._gathered_from_secondary = True
+                else:
+                    self._refresh_gather_input()
+                    assert self._ag_input is not None
+                    cc.backend.all_gather(self._data_flat, self._ag_input, self.process_group)
+                    self._gathered_from_secondary = False
                 self._ag_event = st.record(stream)
             self._unshard_pending = True
 
@@ -564,6 +610,10 @@ class ParamGroup:
         assert self.comm_ctx is not None and self.comm_ctx.streams is not None
         self.comm_ctx.streams.wait_event(None, self._ag_event)
         self._ag_event = None
+        if (self.secondary_group is not None and not self._alias_data and not getattr(self, "_gathered_from_secondary", False)
+                and self._training_state == TrainingState.FORWARD and self.reshard_after_forward and torch.is_grad_enabled()
+                and not is_backward_running()):
+            self._save_secondary_shard()
         if self._has_extensions:
             self._run_post_all_gather_hooks()
         for sp in self.params:
@@ -832,6 +882,7 @@ class ParamGroup:
             if self.reshard_after_backward:
                 self.reshard()
         self._post_forward_indices.clear()
+        self._secondary_valid = False
         # an optimizer step normally follows: the compute-dtype copy is re-derived at the next gather unless the fused
         # optimizer writes it itself (it then marks it fresh again)
         self._ag_input_fresh = False

@@ -136,6 +136,103 @@ int launch_rs(PeerPtrs pp, float* dst, long long shard_numel, int rank, int worl
   }
 }
 
+// ---------------------------------------------------------------- NVSwitch multicast (multimem) collectives
+// `mc` is the multicast address of a buffer that every rank of the group has bound at the same offset: a store to it
+// lands in every rank's copy, a multimem.ld_reduce from it returns the element-wise sum over all ranks' copies,
+// computed inside the switch.  Compared with the pull kernels each GPU then receives 1/world of the gradient
+// bytes (the reduced stream only) and sends its parameter shard once instead of once per peer.
+YF_DEVINL float4 mc_ld_reduce_f32x4(const void* p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+YF_DEVINL uint4 mc_ld_reduce_bf16x8(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+YF_DEVINL void mc_st_v4(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// dst[i] (+)= scale * sum over ranks of their buffer[rank * shard + i], the sum taken by the switch.
+constexpr int MC_UNROLL = 4;
+template <bool BF16_WIRE>
+__global__ void __launch_bounds__(256) reduce_scatter_mc_kernel(const char* __restrict__ mc_in, float* __restrict__ dst, long long shard_numel,
+                                                                int rank, float scale, int accumulate, float* __restrict__ sumsq) {
+  constexpr int EPV = BF16_WIRE ? 8 : 4;
+  const long long nvec = shard_numel / EPV;
+  const char* src = mc_in + (long long)rank * shard_numel * (BF16_WIRE ? 2 : 4);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  float ss = 0.f;
+  auto finish = [&](long long v, float4 o) {
+    float4* d4 = reinterpret_cast<float4*>(dst) + v;
+    o.x *= scale; o.y *= scale; o.z *= scale; o.w *= scale;
+    if (accumulate) {
+      const float4 old = *d4;
+      o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+    }
+    ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+    *d4 = o;
+  };
+  for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < nvec; base += MC_UNROLL * stride) {
+    if constexpr (BF16_WIRE) {
+      uint4 raw[MC_UNROLL];
+#pragma unroll
+      for (int u = 0; u < MC_UNROLL; ++u)
+        if (base + u * stride < nvec) raw[u] = mc_ld_reduce_bf16x8(src + (base + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < MC_UNROLL; ++u) {
+        const long long v = base + u * stride;
+        if (v >= nvec) continue;
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] = __uint_as_float(w[j] << 16);
+          f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+        finish(2 * v, make_float4(f[0], f[1], f[2], f[3]));
+        finish(2 * v + 1, make_float4(f[4], f[5], f[6], f[7]));
+      }
+    } else {
+      float4 acc[MC_UNROLL];
+#pragma unroll
+      for (int u = 0; u < MC_UNROLL; ++u)
+        if (base + u * stride < nvec) acc[u] = mc_ld_reduce_f32x4(src + (base + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < MC_UNROLL; ++u)
+        if (base + u * stride < nvec) finish(base + u * stride, acc[u]);
+    }
+  }
+  if (sumsq != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) atomicAdd(sumsq, ss);
+  }
+}
+
+// Every rank's copy of out[rank * shard .. (rank + 1) * shard) = this rank's shard: one multicast store per 16 bytes.
+__global__ void __launch_bounds__(256) allgather_mc_kernel(const uint4* __restrict__ in, char* __restrict__ mc_out, long long shard_vec, int rank) {
+  char* dst = mc_out + (long long)rank * shard_vec * 16;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < shard_vec; base += MC_UNROLL * stride) {
+    uint4 v[MC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < MC_UNROLL; ++u)
+      if (base + u * stride < shard_vec) v[u] = in[base + u * stride];
+#pragma unroll
+    for (int u = 0; u < MC_UNROLL; ++u)
+      if (base + u * stride < shard_vec) mc_st_v4(dst + (base + u * stride) * 16, v[u]);
+  }
+}
+
 // Barrier between GPUs on signal pads.  pad layout: unsigned 64-bit words [slot][MAX_RANKS]; rank k writes
 // `seq` into word [slot][k] of every rank's pad and waits until all words [slot][*] of its own pad have
 // reached `seq`.  Sequence numbers only grow, so pads are never reset.
@@ -220,6 +317,30 @@ extern "C" int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, lo
   const int rc = bf16_wire ? launch_rs<true>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, sumsq, st)
                            : launch_rs<false>(pp, dst, shard_numel, rank, world, scale, accumulate, n_ctas, sumsq, st);
   if (rc != 0) return rc;
+  return -(int)cudaGetLastError();
+}
+
+// Reduce-scatter through the switch: `mc_in` is the multicast address of the (fp32 or bf16) gradient buffer.
+extern "C" int yf_reduce_scatter_mc(const void* mc_in, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate,
+                                    int bf16_wire, int n_ctas, float* sumsq, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || shard_numel <= 0 || (shard_numel % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(mc_in) & 15) || mc_in == nullptr) return -1;
+  if (n_ctas <= 0) n_ctas = 64;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bf16_wire)
+    reduce_scatter_mc_kernel<true><<<n_ctas, 256, 0, st>>>(static_cast<const char*>(mc_in), dst, shard_numel, rank, scale, accumulate, sumsq);
+  else
+    reduce_scatter_mc_kernel<false><<<n_ctas, 256, 0, st>>>(static_cast<const char*>(mc_in), dst, shard_numel, rank, scale, accumulate, sumsq);
+  return -(int)cudaGetLastError();
+}
+
+// All-gather through the switch: this rank's shard is stored once to the multicast address of the output buffer.
+extern "C" int yf_allgather_mc(const void* in, void* mc_out, long long shard_bytes, int rank, int world, int n_ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || shard_bytes <= 0 || (shard_bytes & 15)) return -1;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(mc_out) & 15) || mc_out == nullptr) return -1;
+  if (n_ctas <= 0) n_ctas = 32;
+  allgather_mc_kernel<<<n_ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(in), static_cast<char*>(mc_out),
+                                                                                 shard_bytes / 16, rank);
   return -(int)cudaGetLastError();
 }
 

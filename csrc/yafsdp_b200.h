@@ -72,6 +72,9 @@ int yf_reduce_scatter_pull(void* const* peer_in, float* dst, long long shard_num
                            int accumulate, int bf16_wire, int n_ctas, void* stream);
 int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long shard_numel, int rank, int world, float scale,
                                  int accumulate, int bf16_wire, int n_ctas, float* sumsq, void* stream);
+int yf_reduce_scatter_mc(const void* mc_in, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate,
+                         int bf16_wire, int n_ctas, float* sumsq, void* stream);
+int yf_allgather_mc(const void* in, void* mc_out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
 int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream);
 int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream);
 int yf_flag_set(void* flags, long long index, long long value, void* stream);

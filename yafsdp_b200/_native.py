@@ -159,6 +159,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_allgather_pull": [_P, _P, _L, _I, _I, _I, _P],
         "yf_reduce_scatter_pull": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P],
         "yf_reduce_scatter_pull_sumsq": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P, _P],
+        "yf_reduce_scatter_mc": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P, _P],
+        "yf_allgather_mc": [_P, _P, _L, _I, _I, _I, _P],
         "yf_signal_barrier": [_P, _I, _I, _I, _L, _L, _P],
         "yf_flag_wait": [_P, _L, _L, _L, _P],
         "yf_flag_set": [_P, _L, _L, _P],

@@ -10,6 +10,11 @@ peer's arena (all ranks allocate in the same order with the same sizes).  The ke
   order with fp32 accumulation, applies the averaging factor and accumulates into the sharded gradient
   in the same pass (reference: four separate steps, ``ya_fsdp/_collectives.py:93-218``).
 
+With the ``mc`` transport the arena is bound to an NVSwitch multicast object (allocated through
+``torch.distributed._symmetric_memory``) and the kernels use ``multimem`` instructions instead: the
+reduce-scatter reads the switch-computed sum of all ranks' copies (``multimem.ld_reduce``), the all-gather
+stores each shard once to the multicast address of the layer buffer (``multimem.st``).
+
 Cross-GPU ordering uses signal pads (sequence-numbered flags in peer memory) with bounded waits; a
 wait that runs out sets the library status word, which ``check()`` reads.
 
@@ -46,7 +51,7 @@ class _CudaBuffer:
 class SymmArena:
     """Bump allocator over chunks of IPC-shared device memory mapped by every rank of ``group``."""
 
-    def __init__(self, device: torch.device, group: dist.ProcessGroup, chunk_bytes: int = 1 << 30):
+    def __init__(self, device: torch.device, group: dist.ProcessGroup, chunk_bytes: int = 1 << 30, multicast: bool = False):
         self.device = device
         self.group = group
         self.rank = group.rank()
@@ -54,8 +59,61 @@ class SymmArena:
         self.chunk_bytes = chunk_bytes
         self.chunks: list[tuple[int, int, list[int], torch.Tensor]] = []  # (local base, nbytes, peer bases, tensor)
         self.offset = 0
+        # multicast arena: chunks come from torch's symmetric-memory allocator, which also binds them to an NVSwitch
+        # multicast object; `mc_bases[i]` is the multicast address of chunk i
+        self.multicast = multicast
+        self.mc_bases: list[int] = []
+        self._mc_keep: list[object] = []
+
+    def _new_chunk_multicast(self, nbytes: int) -> bool:
+        """Allocate a chunk that every rank maps and that is bound to a multicast object.  Returns False (on every rank)
+        when this system offers no multicast; the caller then falls back to CUDA IPC chunks."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        ok, err = 1, ""
+        t = h = None
+        try:
+            t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            h = symm_mem.rendezvous(t, self.group)
+            if not int(h.multicast_ptr):
+                ok, err = 0, "no multicast address"
+        except Exception as e:  # noqa: BLE001 - any failure means: no multicast here
+            ok, err = 0, f"{type(e).__name__}: {e}"
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.multicast = False
+            self.last_multicast_error = err
+            return False
+        assert t is not None and h is not None
+        off = int(getattr(h, "offset", 0))
+        bases = [int(p) + off for p in h.buffer_ptrs]
+        if bases[self.rank] != t.data_ptr():
+            raise RuntimeError("symmetric-memory allocation: the local buffer pointer does not match the tensor")
+        t.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.chunks.append((t.data_ptr(), nbytes, bases, t))
+        self.mc_bases.append(int(h.multicast_ptr) + off)
+        self._mc_keep.append(h)
+        self.offset = 0
+        return True
+
+    def mc_ptr(self, t: torch.Tensor) -> int:
+        """Multicast address of a tensor of the arena (0 when the arena has none or the tensor is not part of it)."""
+        if not self.mc_bases:
+            return 0
+        p = t.data_ptr()
+        for (base, nbytes, _, _), mc in zip(self.chunks, self.mc_bases):
+            if base <= p < base + nbytes:
+                return mc + (p - base)
+        return 0
 
     def _new_chunk(self, nbytes: int) -> None:
+        if self.multicast and self._new_chunk_multicast(nbytes):
+            return
+        if self.mc_bases:
+            raise RuntimeError("multicast allocation stopped working after the first chunk")
         lib = _native.lib()
         ptr = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
@@ -117,8 +175,12 @@ class SymmBackend(CommBackend):
         self.group = group
         self.rank = group.rank()
         self.world = group.size()
-        self.arena = SymmArena(device, group, chunk_bytes=int(os.environ.get("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20)
+        default_transport = "ce" if self.world <= 4 else "sm"
+        want = {os.environ.get(k, "").lower() for k in ("YAFSDP_SYMM_TRANSPORT", "YAFSDP_AG_TRANSPORT", "YAFSDP_RS_TRANSPORT")}
+        self.arena = SymmArena(device, group, chunk_bytes=int(os.environ.get("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20,
+                               multicast="mc" in want)
         self.pads = self.arena.alloc(self.N_SLOTS * 16 * 8)
+        self.has_multicast = bool(self.arena.mc_bases)
         self._pad_ptrs = _ptr_array(self.arena.peer_ptrs(self.pads))
         self._seq = [0] * self.N_SLOTS
         self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
@@ -127,12 +189,22 @@ class SymmBackend(CommBackend):
         # Measured on B200 (Llama-2-7B step, ms): 2 ranks ce 124.5 / sm 134.2; 4 ranks ce (one copy stream per peer) 121.4 /
         # sm 146.9; 8 ranks sm (one communication stream) 134.7 / ce with one copy stream 168 / ce with one stream per
         # peer 142.2.  Hence the default: copy engines up to 4 ranks, pull kernels above.
-        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", "ce" if self.world <= 4 else "sm").lower()
+        # "mc": through NVSwitch multicast (multimem): the switch sums the gradient copies and replicates the parameter
+        # shards, so each GPU receives 1/world of the gradient bytes and sends each shard once; needs a multicast arena
+        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", default_transport).lower()
         # the two collectives can use different transports: "ce" all-gather writes straight into the layer buffer and
         # takes no SM; the reduction needs a kernel anyway, which can pull from the peers itself ("sm") or sum
         # copy-engine-filled staging slots ("ce")
         self.ag_transport = os.environ.get("YAFSDP_AG_TRANSPORT", self.transport).lower()
         self.rs_transport = os.environ.get("YAFSDP_RS_TRANSPORT", self.transport).lower()
+        if not self.has_multicast:
+            if "mc" in (self.ag_transport, self.rs_transport) and self.rank == 0:
+                import warnings
+
+                warnings.warn(f"NVSwitch multicast is not available ({getattr(self.arena, 'last_multicast_error', '')}); "
+                              f"using the {default_transport!r} transport", stacklevel=2)
+            self.ag_transport = default_transport if self.ag_transport == "mc" else self.ag_transport
+            self.rs_transport = default_transport if self.rs_transport == "mc" else self.rs_transport
         # pull kernels of the two collectives would compete for the same SM resources if they ran side by side: keep
         # all-gathers and reduce-scatters on one stream then (copy-engine transfers do not have that problem)
         self.prefers_single_comm_stream = self.rs_transport == "sm" and self.ag_transport == "sm"
@@ -148,7 +220,7 @@ class SymmBackend(CommBackend):
 
     # ------------------------------------------------------------------ memory
     def alloc(self, numel: int, dtype: torch.dtype, device: torch.device, kind: str) -> torch.Tensor:
-        if kind == "gather_output":
+        if kind == "gather_output" and self.ag_transport != "mc":
             return torch.empty(numel, dtype=dtype, device=device)  # only this rank reads or writes it
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         return self.arena.alloc(nbytes)[:nbytes].view(dtype)
@@ -211,6 +283,15 @@ class SymmBackend(CommBackend):
     # ------------------------------------------------------------------ collectives
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
         nbytes = inp.numel() * inp.element_size()
+        mc_out = self.arena.mc_ptr(out) if self.ag_transport == "mc" else 0
+        if mc_out:
+            stream = torch.cuda.current_stream().cuda_stream
+            self.barrier(4)  # every rank is done with what its copy of `out` held before
+            with torch.autograd._unsafe_preserve_version_counter(out):
+                rc = _native.lib().yf_allgather_mc(inp.data_ptr(), mc_out, nbytes, self.rank, self.world, self.ag_ctas, stream)
+            kernels._check(rc, "yf_allgather_mc")
+            self.barrier(5)  # every rank's stores have landed in every copy
+            return
         if self.ag_transport == "ce":
             lib = _native.lib()
             stream = torch.cuda.current_stream().cuda_stream
@@ -252,6 +333,10 @@ class SymmBackend(CommBackend):
             rc = lib.yf_reduce_scatter_pull_sumsq(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
                                                   int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
                                                   None if sumsq is None else sumsq.data_ptr(), stream)
+        elif self.rs_transport == "mc" and self.arena.mc_ptr(inp):
+            rc = _native.lib().yf_reduce_scatter_mc(self.arena.mc_ptr(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                    int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
+                                                    None if sumsq is None else sumsq.data_ptr(), stream)
         else:
             rc = _native.lib().yf_reduce_scatter_pull_sumsq(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
                                                             int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,

@@ -288,7 +288,8 @@ def _v1_worker(rank, world):
     local = wrapped.local_state_dict()
     assert "main_parameter" in local and "layernorm_parameter" in local and (("meta" in local) == (rank == 0))
     if rank == 0:
-        assert "main_parameter_shard_bounaries" in local["meta"] and len(local["meta"]["main_shards_fqns"]) == 6
+        assert "main_parameter_shard_bounaries" in local["meta"] and len(local["meta"]["main_shards_fqns"]) == 5
+        assert local["meta"]["layernorm_fqns"] == [["norm.weight", "norm.bias"]]
     full = wrapped.state_dict()
     if rank == 0:
         assert set(full) == set(_build().state_dict()) and full["emb.weight"].shape == (32, 16)
@@ -411,3 +412,99 @@ def _hpz_worker(rank, world):
 @pytest.mark.timeout(240)
 def test_hierarchical_partitioning_secondary_shards():
     run_distributed(_hpz_worker, 4)
+
+
+# ------------------------------------------------------------------------------------------------
+class NormBlock(nn.Module):
+    def __init__(self, d=16, h=24):
+        super().__init__()
+        self.ln = nn.LayerNorm(d)
+        self.a = nn.Linear(d, h)
+        self.b = nn.Linear(h, d)
+
+    def forward(self, x):
+        return x + self.b(torch.relu(self.a(self.ln(x))))
+
+
+class NormNet(Net):
+    def __init__(self, n_layers=3, d=16, vocab=32):
+        super().__init__(n_layers, d, vocab)
+        self.layers = nn.ModuleList([NormBlock(d) for _ in range(n_layers)])
+
+
+def _norm_net(seed=0):
+    torch.manual_seed(seed)
+    return NormNet()
+
+
+def _v1_norm_group_worker(rank, world):
+    """All norm weights form one group (gathered once per step, own buffers); inference mode keeps no gradient buffers."""
+    from yafsdp_b200.comm import backends
+    from yafsdp_b200.compat_v1 import YaFSDP
+    from yafsdp_b200.optim import param_groups_of
+
+    def wrap(model, **kw):
+        return YaFSDP(
+            model, zero_stage=3, param_dtype=torch.float32,
+            modules_to_wrap_with_names=[(model.emb, "emb")] + [(l, f"layers.{i}") for i, l in enumerate(model.layers)] + [(model.head, "head")],
+            layer_norm_module_cls=nn.LayerNorm, gradient_accumulation_steps=1,
+            rogue_layer_norm_modules_with_names={model.norm: "norm"}, comm_backend="torch", **kw,
+        )
+
+    ref = _norm_net()
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=1e-2)
+    for _ in range(2):
+        ref_opt.zero_grad()
+        for r in range(world):
+            (_loss(ref, _data(r * 10)) / world).backward()
+        ref_opt.step()
+
+    model = _norm_net()
+    wrapped = wrap(model)
+    groups = param_groups_of(model)
+    norm_groups = [g for g in groups if getattr(g, "is_norm_group", False)]
+    assert len(norm_groups) == 1 and len(norm_groups[0].params) == 2 * 4 and len(groups) == 6
+    gathers = []
+    orig = backends.TorchBackend.all_gather
+
+    def spy(self, out, inp, group):
+        gathers.append(out.numel())
+        return orig(self, out, inp, group)
+
+    backends.TorchBackend.all_gather = spy
+    params = list(wrapped.parameters())
+    opt = torch.optim.SGD(params, lr=1e-2)
+    for _ in range(2):
+        gathers.clear()
+        wrapped.zero_grad()
+        _loss(wrapped, _data(rank * 10)).backward()
+        opt.step()
+        assert gathers.count(norm_groups[0].layout.padded_numel) == 1, gathers  # the norm group is gathered once per step
+    backends.TorchBackend.all_gather = orig
+    _check_params(model, {n: p.detach() for n, p in ref.named_parameters()})
+    local = wrapped.local_state_dict()
+    assert local["layernorm_parameter"].numel() == norm_groups[0].layout.shard_numel
+    if rank == 0:
+        assert local["meta"]["layernorm_fqns"][0][0] == "layers.0.ln.weight" and len(local["meta"]["main_shards_fqns"]) == 5
+    before = [p.detach().clone() for p in params]
+    with torch.no_grad():
+        for p in params:
+            p.zero_()
+    wrapped.load_state_dict(local)
+    assert all(torch.equal(a, b) for a, b in zip(before, params))
+
+    # ---- inference mode
+    frozen = _norm_net()
+    want = frozen(_data(rank))
+    inf = wrap(frozen, is_trainable=False)
+    with torch.no_grad():
+        got = inf(_data(rank))
+    assert torch.allclose(got, want, atol=1e-6)
+    state = frozen._get_fsdp_state()
+    assert all(ctx.tensor is None for ctx in state._grad_ctxs)
+    assert all(not p.requires_grad for p in inf.parameters())
+
+
+@pytest.mark.timeout(240)
+def test_v1_norm_group_and_inference_mode():
+    run_distributed(_v1_norm_group_worker, 2)

@@ -141,16 +141,25 @@ def full_state_dict(model: nn.Module, rank0_only: bool = True) -> dict[str, torc
     return out
 
 
+def _split_norm_group(model: nn.Module) -> tuple[list[Any], list[Any]]:
+    groups = param_groups_of(model)
+    return [g for g in groups if not getattr(g, "is_norm_group", False)], [g for g in groups if getattr(g, "is_norm_group", False)]
+
+
 def local_state_dict_v1(model: nn.Module) -> dict[str, Any]:
     """Per-rank local checkpoint in the first-generation layout: ``"main_parameter"`` is the concatenation of this rank's flat
-    shard of every group (in wrap order), ``"layernorm_parameter"`` is empty here (norm weights live inside their layer's
-    group), and rank 0 adds ``"meta"`` with the shard sizes, padded sizes and per-group parameter names, sizes and shapes
-    (key spellings as in the reference, including ``main_parameter_shard_bounaries``)."""
-    groups = param_groups_of(model)
+    shard of every wrapped group (in wrap order), ``"layernorm_parameter"`` this rank's flat shard of the norm group (empty
+    when the model was wrapped without one), and rank 0 adds ``"meta"`` with the shard sizes, padded sizes and per-group
+    parameter names, sizes and shapes (key spellings as in the reference, including ``main_parameter_shard_bounaries``)."""
+    groups, norm = _split_norm_group(model)
+    dev = groups[0].device if groups else torch.device("cpu")
     sd: dict[str, Any] = {
         "main_parameter": torch.cat([g.master_flat.detach().reshape(-1) for g in groups]) if groups else torch.empty(0),
-        "layernorm_parameter": torch.empty(0),
+        "layernorm_parameter": torch.cat([g.master_flat.detach().reshape(-1) for g in norm]) if norm else torch.empty(0, device=dev),
     }
+    for name, buf in model.named_buffers():
+        if name.rpartition(".")[2] not in getattr(model.get_submodule(name.rpartition(".")[0]), "_non_persistent_buffers_set", ()):
+            sd["module." + name] = buf
     rank = dist.get_rank() if dist.is_initialized() else 0
     if rank == 0:
         sd["meta"] = {
@@ -159,9 +168,9 @@ def local_state_dict_v1(model: nn.Module) -> dict[str, Any]:
             "main_shards_fqns": [[sp.fqn or sp.info.param_name for sp in g.params] for g in groups],
             "main_shards_numels": [[sp.numel for sp in g.params] for g in groups],
             "main_parameter_orig_shapes": [[tuple(sp.orig_shape) for sp in g.params] for g in groups],
-            "layernorm_fqns": [],
-            "layernorm_numels": [],
-            "layernorm_orig_shapes": [],
+            "layernorm_fqns": [[sp.fqn or sp.info.param_name for sp in g.params] for g in norm],
+            "layernorm_numels": [[sp.numel for sp in g.params] for g in norm],
+            "layernorm_orig_shapes": [[tuple(sp.orig_shape) for sp in g.params] for g in norm],
         }
     return sd
 
@@ -170,13 +179,19 @@ def load_local_state_dict_v1(model: nn.Module, sd: dict[str, Any]) -> None:
     """Inverse of :func:`local_state_dict_v1` (same world size and padding only, like the reference)."""
     sd = dict(sd)
     sd.pop("meta", None)
-    flat = sd["main_parameter"]
-    o = 0
+    groups, norm = _split_norm_group(model)
     with torch.no_grad():
-        for g in param_groups_of(model):
-            n = g.layout.shard_numel
-            g.master_flat.copy_(flat[o : o + n])
-            g._ag_input_fresh = False
-            o += n
-    if o != flat.numel():
-        raise ValueError(f"local state dict has {flat.numel()} elements, the model's shards hold {o}")
+        for key, gs in (("main_parameter", groups), ("layernorm_parameter", norm)):
+            flat = sd[key]
+            o = 0
+            for g in gs:
+                n = g.layout.shard_numel
+                g.master_flat.copy_(flat[o : o + n])
+                g._ag_input_fresh = False
+                o += n
+            if o != flat.numel():
+                raise ValueError(f"local state dict entry {key!r} has {flat.numel()} elements, the model's shards hold {o}")
+        buffers = dict(model.named_buffers())
+        for k, v in sd.items():
+            if k.startswith("module.") and k[len("module."):] in buffers:
+                buffers[k[len("module."):]].copy_(v)

@@ -4,8 +4,10 @@ Parity: ``ya_fsdp/ya_fsdp.py:70-602`` (``YaFSDP``), the argument mapping of ``do
 The class maps the old arguments onto the same core that ``fully_shard`` uses:
 
 * every ``(module, name)`` of ``modules_to_wrap_with_names`` becomes one parameter group (the reference's
-  ``SuperTensorModule``); parameters outside them (e.g. a final norm listed in
-  ``rogue_layer_norm_modules_with_names``) form further groups; the wrapped model is the parameter-less root;
+  ``SuperTensorModule``); all modules of ``layer_norm_module_cls`` plus those of
+  ``rogue_layer_norm_modules_with_names`` form ONE further group with buffers of its own, gathered once per forward
+  and kept until the end of backward (the reference's norm super-tensor); the wrapped model is the root;
+* ``is_trainable=False``: the model is kept in ``param_dtype`` with no master copy and no gradient buffers;
 * ``zero_stage=3``: gathered weights are freed after use (two rotating weight buffers); ``zero_stage<=2``:
   weights stay gathered after the first use (one buffer per group);
 * ``bit16_reduce_scatter`` / ``bit32_acc_for_bit16_reduce_scatter`` select the reduce dtype; gradients are
@@ -99,32 +101,50 @@ class YaFSDP(nn.Module):
         self._dp_size = pg.size()
 
         reduce_dtype = torch.bfloat16 if bit16_reduce_scatter else torch.float32
+        dev = torch.device(device_type, torch.cuda.current_device()) if device_type == "cuda" else torch.device("cpu")
+        rogue = rogue_layer_norm_modules_with_names or []
+        rogue_items = list(rogue.items()) if isinstance(rogue, dict) else list(rogue)
+        # materialise / synchronise first: the norm modules inside the wrapped modules are sharded before their parents
+        for sub in [m for m, _ in modules_to_wrap_with_names] + [m for m, _ in rogue_items]:
+            if param_init_fn is not None and any(p.device.type == "meta" for p in sub.parameters()):
+                sub.to_empty(device=dev)
+                param_init_fn(sub)
+            if sync_module_states:
+                _broadcast_module(sub, pg)
+        if not is_trainable:
+            # inference: no fp32 master and no gradient buffers; the flat parameters are kept in param_dtype and are the
+            # all-gather input themselves (ya_fsdp/ya_fsdp.py:355-360)
+            module.to(param_dtype)
+            module.requires_grad_(False)
         policy = MixedPrecisionPolicy(
-            param_dtype=param_dtype,
-            reduce_dtype=reduce_dtype,
-            bit32_acc_for_bit16_reduce_scatter=bool(bit16_reduce_scatter and bit32_acc_for_bit16_reduce_scatter),
+            param_dtype=param_dtype if is_trainable else None,
+            reduce_dtype=reduce_dtype if is_trainable else None,
+            bit32_acc_for_bit16_reduce_scatter=bool(is_trainable and bit16_reduce_scatter and bit32_acc_for_bit16_reduce_scatter),
         )
         reshard = zero_stage >= 3
         # with zero_stage <= 2 nobody reshards after forward, so every group gets its own weight buffer
         kw: dict[str, Any] = dict(mesh=mesh, mp_policy=policy, reshard_after_forward=reshard if reshard else False)
 
+        # ---- all norm weights of the model form ONE group that is gathered once per forward and stays gathered until the end
+        # of backward (the reference's "layernorm super-tensor", ya_fsdp/ya_fsdp.py:313-323,469-471), in its own buffers
+        wrapped_set = {m for m, _ in modules_to_wrap_with_names}
+        norm_modules: list[nn.Module] = []
+        if layer_norm_module_cls is not None:
+            norm_modules = [m for m in module.modules() if isinstance(m, layer_norm_module_cls) and m not in wrapped_set]
+        for m, _ in rogue_items:
+            if m not in norm_modules and m not in wrapped_set:
+                norm_modules.append(m)
+        norm_modules = [m for m in norm_modules if next(m.parameters(), None) is not None]
+        self._norm_group: Any = None
+        if norm_modules:
+            fully_shard(norm_modules if len(norm_modules) > 1 else norm_modules[0], **{**kw, "reshard_after_forward": False})
+            self._norm_group = norm_modules[0]._get_fsdp_state()._param_group  # type: ignore[attr-defined]
+            self._norm_group.dedicated_buffers = True
+            self._norm_group.is_norm_group = True
         wrapped: list[nn.Module] = []
         for sub, _name in modules_to_wrap_with_names:
-            if param_init_fn is not None and any(p.device.type == "meta" for p in sub.parameters()):
-                sub.to_empty(device=torch.device(device_type, torch.cuda.current_device()) if device_type == "cuda" else "cpu")
-                param_init_fn(sub)
-            if sync_module_states:
-                _broadcast_module(sub, pg)
             fully_shard(sub, **kw)
             wrapped.append(sub)
-        rogue = rogue_layer_norm_modules_with_names or []
-        rogue_items = list(rogue.items()) if isinstance(rogue, dict) else list(rogue)
-        rogue_modules = [m for m, _ in rogue_items if m not in wrapped]
-        if rogue_modules:
-            if sync_module_states:
-                for m in rogue_modules:
-                    _broadcast_module(m, pg)
-            fully_shard(rogue_modules if len(rogue_modules) > 1 else rogue_modules[0], **kw)
         leftover = [p for p in module.parameters() if not hasattr(p, "_spec")]
         if leftover:
             warnings.warn(f"{len(leftover)} parameters are outside the wrapped modules; they are sharded with the root group", stacklevel=2)

@@ -366,6 +366,8 @@ class ParamGroup:
         self._norm_fused_ok = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
+        # True: this group never shares its gather / reduce buffers with the rotating ones
+        self.dedicated_buffers = False
         # hierarchical partitioning: a secondary shard of the gathered weights kept inside a smaller (intra-node) group
         self.secondary_group: dist.ProcessGroup | None = None
         self._secondary_shard: torch.Tensor | None = None
@@ -486,7 +488,10 @@ class ParamGroup:
         data_flat = self._ag_input if self._alias_data else data_ctx.view(self.all_gather_dtype, self.layout.padded_numel)
         # unsharded gradient storage
         self._alias_grad = single and self.reduce_scatter_dtype == self.orig_dtype
-        grad_flat = self.sharded_grad_flat if self._alias_grad else grad_ctx.view(self.reduce_scatter_dtype, self.layout.padded_numel)
+        trainable = any(sp.requires_grad for sp in self.params)
+        grad_flat = None
+        if trainable:
+            grad_flat = self.sharded_grad_flat if self._alias_grad else grad_ctx.view(self.reduce_scatter_dtype, self.layout.padded_numel)
         self._data_flat = data_flat
         self._grad_flat = grad_flat
         for sp in self.params:
@@ -500,7 +505,7 @@ class ParamGroup:
             sp.gathered_view = view
             # extension parameters get their unsharded tensor from fsdp_post_all_gather at the first unshard
             sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad) if sp.ext_cls is None else None
-            sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape)
+            sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape) if grad_flat is not None else None
             # kernels write fp32 gradients into the sink; with a 16-bit reduce dtype the autograd .grad path is used instead
             sp.sink = (GradSink(self, sp.index, sp.rs_view)
                        if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 and sp.outer_mesh is None

@@ -214,13 +214,25 @@ class FSDPState:
         if not groups:
             return
         # ---- data buffers: two per process group, or one per group when nobody reshards after forward
-        nobody_reshards = all(not g.reshard_after_forward for g in groups)
+        nobody_reshards = all(not g.reshard_after_forward for g in groups if not g.dedicated_buffers)
         by_pg: dict[Any, list[ParamGroup]] = {}
         for g in groups:
             by_pg.setdefault(g.process_group, []).append(g)
         self._data_ctxs: list[BufferContext] = []
         self._grad_ctxs: list[BufferContext] = []
-        for pg_groups in by_pg.values():
+        for all_pg_groups in by_pg.values():
+            # a group that stays gathered while others come and go (e.g. all norm weights of a model) owns its buffers
+            for g in all_pg_groups:
+                if g.dedicated_buffers:
+                    g.data_ctx = BufferContext("data", len(self._data_ctxs))
+                    g.grad_ctx = BufferContext("grad", len(self._grad_ctxs))
+                    g.data_ctx.users.append(g)
+                    g.grad_ctx.users.append(g)
+                    self._data_ctxs.append(g.data_ctx)
+                    self._grad_ctxs.append(g.grad_ctx)
+            pg_groups = [g for g in all_pg_groups if not g.dedicated_buffers]
+            if not pg_groups:
+                continue
             n_data = len(pg_groups) if nobody_reshards else min(2, len(pg_groups))
             n_grad = len(pg_groups) if allow_no_grad_reduce else min(max(1, num_grad_buffers or 1), len(pg_groups))
             data = [BufferContext("data", len(self._data_ctxs) + i) for i in range(n_data)]
@@ -239,7 +251,8 @@ class FSDPState:
             if users:
                 ctx.lazy_init(max(g.data_buffer_nbytes() for g in users), self._device, backend)
         for ctx in self._grad_ctxs:
-            users = [g for g in ctx.users if not (g.world_size == 1 and g.reduce_scatter_dtype == g.orig_dtype)]
+            users = [g for g in ctx.users if not (g.world_size == 1 and g.reduce_scatter_dtype == g.orig_dtype)
+                     and any(sp.requires_grad for sp in g.params)]
             if users:
                 ctx.lazy_init(max(g.grad_buffer_nbytes() for g in users), self._device, backend)
         # ---- auto mode: the last user of every data buffer keeps its parameters after forward, because

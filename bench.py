@@ -20,6 +20,7 @@ import os
 import statistics
 import subprocess
 import sys
+import time
 
 import torch
 import torch.distributed as dist
@@ -145,6 +146,14 @@ def run(args, make_step) -> dict:
     step_e2e(host_batches[0])  # one untimed pass through the end-to-end path
     ms_e2e = timed_steps(step_e2e, host_batches, args.steps, device, finish)
     clocks = sampler.stop() if rank == 0 else {}
+    # host time to issue one step into an empty queue (no device wait inside): when it approaches ms_per_step the step is
+    # bound by the launching CPU thread, not by the GPU
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    step_dev(dev_batches[0])
+    host_issue_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, device)
+    torch.cuda.synchronize()
     tokens = batch * seq * world * args.steps
     value = tokens / (ms / 1e3)
     e2e_value = tokens / (ms_e2e / 1e3)
@@ -185,6 +194,7 @@ def run(args, make_step) -> dict:
         "gpu_launches": int(launches),
         "tokens_per_s_per_gpu": round(value / world, 1),
         "peak_mem_gb": round(peak_gb, 2),
+        "host_issue_ms_per_step": round(host_issue_ms, 2),
     }
     if rank == 0:
         print(json.dumps(result), flush=True)

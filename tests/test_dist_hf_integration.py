@@ -1,0 +1,69 @@
+"""Hugging Face integration on CPU/gloo (world 2): a tiny ``LlamaForCausalLM`` sharded through ``shard_causal_lm`` (both APIs,
+tied and untied embeddings, activation checkpointing, weights only on rank 0) trains like the unsharded model."""
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+transformers = pytest.importorskip("transformers")
+
+
+def _tiny(tie=False, meta=False):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    cfg = LlamaConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                      vocab_size=64, max_position_embeddings=64, tie_word_embeddings=tie, attn_implementation="eager")
+    torch.manual_seed(0)
+    if meta:
+        with torch.device("meta"):
+            return LlamaForCausalLM(cfg)
+    return LlamaForCausalLM(cfg)
+
+
+def _ids(rank):
+    return torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(7 + rank))
+
+
+def _reference(world, steps, tie):
+    model = _tiny(tie)
+    opt = torch.optim.SGD(model.parameters(), lr=5e-2)
+    for _ in range(steps):
+        opt.zero_grad()
+        for r in range(world):
+            ids = _ids(r)
+            (model(input_ids=ids, labels=ids).loss / world).backward()
+        opt.step()
+    return {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+def _worker(rank, world, api, tie):
+    from yafsdp_b200 import MixedPrecisionPolicy
+    from yafsdp_b200.integrations.hf import find_decoder_parts, shard_causal_lm, trainer_callbacks
+
+    model = _tiny(tie, meta=rank != 0)  # weights exist on rank 0 only
+    parts = find_decoder_parts(model)
+    assert len(parts.layers) == 3 and parts.tied == tie and parts.name(parts.layers[1]) == "model.layers.1"
+    wrapped = shard_causal_lm(model, mp_policy=MixedPrecisionPolicy(), num_layers_to_checkpoint=2, sync_from_rank0=True,
+                              api=api, comm_backend="torch")
+    params = list(wrapped.parameters())
+    opt = torch.optim.SGD(params, lr=5e-2)
+    for _ in range(2):
+        if api == "v1":
+            wrapped.zero_grad()
+        else:
+            opt.zero_grad()
+        ids = _ids(rank)
+        wrapped(input_ids=ids, labels=ids).loss.backward()
+        opt.step()
+    want = _reference(world, 2, tie)
+    for n, p in model.named_parameters():
+        full = p.full_tensor() if hasattr(p, "full_tensor") else p.detach()
+        assert torch.allclose(full, want[n], atol=2e-5), n
+    assert len(trainer_callbacks()) == 1 and len(trainer_callbacks(trace_path="t.json", memory_snapshot_path="m")) == 3
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("api,tie", [("fully_shard", False), ("fully_shard", True), ("v1", False)])
+def test_hf_causal_lm(api, tie):
+    run_distributed(_worker, 2, api, tie)

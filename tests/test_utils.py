@@ -51,3 +51,27 @@ def test_checkpoint_module_recomputes():
     x = torch.randn(2, 4, requires_grad=True)
     m(x).sum().backward()
     assert len(calls) == 2 and m.l.weight.grad is not None  # forward ran again during backward
+
+
+def test_trainer_config_file_provides_defaults_and_flags_override():
+    import argparse
+    import os
+
+    from yafsdp_b200.train import parse_with_config
+
+    def parser():
+        ap = argparse.ArgumentParser()
+        ap.add_argument("--model", default="llama2-7b")
+        ap.add_argument("--seq-len", type=int, default=2048)
+        ap.add_argument("--checkpoint-layers", type=int, default=0)
+        ap.add_argument("--steps", type=int, default=10)
+        ap.add_argument("--batch", type=int, default=1)
+        ap.add_argument("--lr", type=float, default=3e-4)
+        ap.add_argument("--max-grad-norm", type=float, default=1.0)
+        ap.add_argument("--comm-backend", default="auto")
+        ap.add_argument("--config", default=None)
+        return ap
+
+    cfg = os.path.join(os.path.dirname(__file__), "..", "examples", "shard_config.yaml")
+    args = parse_with_config(parser(), ["--config", cfg, "--seq-len", "4096"])
+    assert args.steps == 100 and args.seq_len == 4096 and args.model == "llama2-7b" and args.checkpoint_layers == 0

@@ -10,8 +10,12 @@ What is supported (and what is not) mirrors the reference:
   ``allow_no_grad_reduce=True`` at lazy init together with ``set_requires_gradient_sync``;
 * gradient accumulation, mixed precision, activation checkpointing, hooks for external pipeline schedules.
 
-Not implemented, as in the reference: tensor / pipeline / sequence / context parallelism, hybrid (2-D) sharding.
-Parameters that already are ``DTensor``s of an external tensor- or expert-parallel mesh are not accepted yet.
+* hierarchical partitioning (secondary shards inside a smaller group for the backward gather):
+  ``module.set_secondary_shard_group(group)``;
+* parameters that already are ``DTensor``s of an external tensor- or expert-parallel mesh: their local tensors are
+  sharded over the data-parallel mesh and gathered back as ``DTensor``s of the outer mesh.
+
+Not implemented, as in the reference: tensor / pipeline / sequence / context parallelism themselves, hybrid (2-D) sharding.
 """
 
 from __future__ import annotations

@@ -89,12 +89,16 @@ class FSDPState:
         modules_set = set(modules)
 
         def pre(module: nn.Module, args: Any, kwargs: Any) -> Any:
+            if self._training_state == TrainingState.PRE_BACKWARD:
+                return None  # activation-checkpoint recompute of some of the modules: not a forward pass of the group
             if not self._modules_to_run_forward:
                 self._modules_to_run_forward = set(modules_set)
                 return self._pre_forward(module, args, kwargs)
             return None
 
         def post(module: nn.Module, args: Any, output: Any) -> Any:
+            if self._training_state == TrainingState.PRE_BACKWARD:
+                return None
             self._modules_to_run_forward.discard(module)
             if not self._modules_to_run_forward:
                 return self._post_forward(module, args, output)

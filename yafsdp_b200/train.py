@@ -114,6 +114,25 @@ def smoke_step(device: torch.device) -> float:
             dist.destroy_process_group()
 
 
+def parse_with_config(ap: argparse.ArgumentParser, argv: list[str] | None = None) -> argparse.Namespace:
+    """``--config file.yaml`` provides defaults (keys = option names, dashes or underscores); explicit flags override them."""
+    pre, _ = ap.parse_known_args(argv)
+    if getattr(pre, "config", None):
+        import yaml
+
+        with open(pre.config) as f:
+            values = yaml.safe_load(f) or {}
+        known = {a.dest for a in ap._actions}
+        defaults = {}
+        for k, v in values.items():
+            dest = str(k).replace("-", "_")
+            if dest not in known:
+                raise SystemExit(f"{pre.config}: unknown option {k!r}")
+            defaults[dest] = v
+        ap.set_defaults(**defaults)
+    return ap.parse_args(argv)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description="Train a Llama-family model on synthetic tokens with sharded data parallelism")
     ap.add_argument("--model", default="llama2-7b", choices=sorted(CONFIGS))
@@ -124,7 +143,8 @@ def main() -> None:
     ap.add_argument("--max-grad-norm", type=float, default=1.0)
     ap.add_argument("--checkpoint-layers", type=int, default=0)
     ap.add_argument("--comm-backend", default="auto", choices=["auto", "torch", "symm"])
-    args = ap.parse_args()
+    ap.add_argument("--config", default=None, help="YAML file with defaults for the options above (command line wins)")
+    args = parse_with_config(ap)
     rank, world, device = init_distributed()
     cfg = CONFIGS[args.model]
     model = build_llama(cfg, device, comm_backend=args.comm_backend, checkpoint_layers=args.checkpoint_layers)

@@ -508,3 +508,58 @@ def _v1_norm_group_worker(rank, world):
 @pytest.mark.timeout(240)
 def test_v1_norm_group_and_inference_mode():
     run_distributed(_v1_norm_group_worker, 2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _v1_model_parallel_worker(rank, world):
+    """2 data-parallel x 2 model-parallel ranks: norm gradients are summed over the model-parallel group after the
+    data-parallel reduction; the clipping norm is taken over both groups."""
+    import torch.distributed as dist
+    from yafsdp_b200.compat_v1 import YaFSDP
+    from yafsdp_b200.optim import param_groups_of
+
+    dp = mp = None
+    for ranks in ([0, 1], [2, 3]):
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            dp = g
+    for ranks in ([0, 2], [1, 3]):
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            mp = g
+    model = _norm_net()
+    wrapped = YaFSDP(
+        model, zero_stage=3, param_dtype=torch.float32,
+        modules_to_wrap_with_names=[(model.emb, "emb")] + [(l, f"layers.{i}") for i, l in enumerate(model.layers)] + [(model.head, "head")],
+        layer_norm_module_cls=nn.LayerNorm, gradient_accumulation_steps=1, rogue_layer_norm_modules_with_names={model.norm: "norm"},
+        data_parallel_process_group=dp, model_parallel_process_group=mp, all_reduce_grads_across_model_parallel_group=True,
+        comm_backend="torch",
+    )
+    list(wrapped.parameters())
+    wrapped.zero_grad()
+    _loss(wrapped, _data(rank * 10)).backward()
+
+    ref = _norm_net()
+    grads = []
+    for r in range(world):
+        ref.zero_grad()
+        _loss(ref, _data(r * 10)).backward()
+        grads.append({n: p.grad.clone() for n, p in ref.named_parameters()})
+    my_dp = [0, 1] if rank < 2 else [2, 3]
+    for n, p in model.named_parameters():
+        got = p.grad.full_tensor()
+        if ".ln." in n or n.startswith("norm."):
+            want = sum(grads[r][n] for r in range(world)) / 2  # mean over each data-parallel pair, summed over the pairs
+        else:
+            want = sum(grads[r][n] for r in my_dp) / 2
+        assert torch.allclose(got, want, atol=1e-6), n
+    local_sq = sum(g.sharded_grad_flat.double().pow(2).sum() for g in param_groups_of(model))
+    tot = torch.tensor([float(local_sq)], dtype=torch.float64)
+    dist.all_reduce(tot)
+    norm = wrapped.clip_grad_norm_(1e9)
+    assert abs(norm.item() - tot.sqrt().item()) < 1e-4 * tot.sqrt().item()
+
+
+@pytest.mark.timeout(240)
+def test_v1_norm_gradients_summed_over_model_parallel_group():
+    run_distributed(_v1_model_parallel_worker, 4)

@@ -20,6 +20,10 @@ The class maps the old arguments onto the same core that ``fully_shard`` uses:
   gathered to CPU on rank 0) and ``zero_grad`` (``set_to_none=True`` refused: the gradients are persistent flat
   buffers) behave as in the reference.
 
+``model_parallel_process_group``: the wrapper shards over the data-parallel group only; with
+``all_reduce_grads_across_model_parallel_group`` the norm group's reduced gradients are summed over the model-parallel
+group, and ``clip_grad_norm_`` adds the squared norms over it.
+
 Not carried over: the closed-source communication library switches (``use_yccl*``: accepted and ignored with
 a warning; the peer-memory backend plays that role, ``comm_backend="symm"``), ``yccl_intra_inter_expr`` (an
 ``eval`` of a user string).  ``hpz_first_layers_num`` keeps a secondary shard of the first layers' weights inside
@@ -77,8 +81,9 @@ class YaFSDP(nn.Module):
             raise ValueError("hpz_first_layers_num needs zero_stage=3: with weights kept gathered there is no backward all-gather")
         if use_yccl or yccl_intra_inter_expr is not None or yccl_all_gather_stages is not None:
             warnings.warn("the closed-source communication library options are ignored; use comm_backend='symm'", stacklevel=2)
-        if model_parallel_process_group is not None and model_parallel_process_group.size() > 1:
-            raise NotImplementedError("composition with an external model-parallel group is not implemented")
+        if all_reduce_grads_across_model_parallel_group and model_parallel_process_group is None:
+            raise ValueError("all_reduce_grads_across_model_parallel_group needs model_parallel_process_group")
+        self._mp_group = model_parallel_process_group
         if not modules_to_wrap_with_names:
             raise ValueError("modules_to_wrap_with_names must list the (module, name) pairs to shard as units")
         self.module = module
@@ -141,6 +146,11 @@ class YaFSDP(nn.Module):
             self._norm_group = norm_modules[0]._get_fsdp_state()._param_group  # type: ignore[attr-defined]
             self._norm_group.dedicated_buffers = True
             self._norm_group.is_norm_group = True
+            if all_reduce_grads_across_model_parallel_group and self._mp_group is not None and self._mp_group.size() > 1:
+                # norm weights are replicated over the model-parallel group and see different activations there:
+                # their reduced gradients are summed over it (ya_fsdp/ya_fsdp.py:989-990)
+                mp = self._mp_group
+                self._norm_group.post_reduce_hook = lambda shard: dist.all_reduce(shard, group=mp)
         wrapped: list[nn.Module] = []
         for sub, _name in modules_to_wrap_with_names:
             fully_shard(sub, **kw)
@@ -206,6 +216,8 @@ class YaFSDP(nn.Module):
             total = total + g.sharded_grad_flat.float().pow(2).sum()
         if self._dp_size > 1:
             dist.all_reduce(total, group=groups[0].process_group)
+        if self._mp_group is not None and self._mp_group.size() > 1:
+            dist.all_reduce(total, group=self._mp_group)
         total = total.sqrt()
         coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
         for g in groups:

@@ -284,6 +284,13 @@ class YaFSDPModule:
             if s._param_group is not None:
                 s._param_group.force_sum_reduction_for_comms = enable
 
+    def set_post_reduce_hook(self, hook: Any) -> None:
+        """``hook(flat_shard)`` runs on the reduce-scatter stream on this rank's reduced flat gradient shard of every
+        micro-batch, before accumulation (the place where the reference all-reduces norm gradients over the
+        model-parallel group, ``ya_fsdp/ya_fsdp.py:989-990``; upstream FSDP2 calls it ``set_all_reduce_hook``)."""
+        if (g := self._get_fsdp_state()._param_group) is not None:
+            g.post_reduce_hook = hook
+
     def set_secondary_shard_group(self, group: Any, *, recurse: bool = False) -> None:
         """Hierarchical partitioning for this module's parameter group: gather the weights for backward inside ``group``
         (e.g. the ranks of one node) from a secondary shard saved after the forward all-gather."""

@@ -366,6 +366,9 @@ class ParamGroup:
         self._norm_fused_ok = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
+        # called on the reduce-scatter stream with this rank's freshly reduced flat gradient shard (before it is
+        # accumulated into the sharded gradient)
+        self.post_reduce_hook: Callable[[torch.Tensor], None] | None = None
         # True: this group never shares its gather / reduce buffers with the rotating ones
         self.dedicated_buffers = False
         # hierarchical partitioning: a secondary shard of the gathered weights kept inside a smaller (intra-node) group
@@ -835,7 +838,7 @@ class ParamGroup:
             if pre is not None and pre != 1.0:
                 self._grad_flat.div_(pre)
             dst = self.sharded_grad_flat
-            if all_fresh or all_have:
+            if (all_fresh or all_have) and self.post_reduce_hook is None:
                 # the reduction kernel can also sum the squares of the final shard (gradient-norm fusion) when this is the
                 # only contribution of the step to the sharded gradient
                 target = self._norm_sq if (self._norm_sq is not None and all_fresh and dst.dtype == torch.float32) else None
@@ -851,6 +854,8 @@ class ParamGroup:
                 self._norm_fused_ok = False
                 own = self._grad_flat[self.rank * self.layout.shard_numel : (self.rank + 1) * self.layout.shard_numel]
                 self.comm_ctx.backend.reduce_scatter(own, self._grad_flat, self.process_group, scale=scale, accumulate=False)
+                if self.post_reduce_hook is not None:
+                    self.post_reduce_hook(own)  # e.g. an all-reduce of this micro-batch's reduced shard over another group
                 for sp in with_grad:
                     pl = sp.placement
                     assert pl is not None

@@ -75,3 +75,19 @@ def test_trainer_config_file_provides_defaults_and_flags_override():
     cfg = os.path.join(os.path.dirname(__file__), "..", "examples", "shard_config.yaml")
     args = parse_with_config(parser(), ["--config", cfg, "--seq-len", "4096"])
     assert args.steps == 100 and args.seq_len == 4096 and args.model == "llama2-7b" and args.checkpoint_layers == 0
+
+
+def test_memory_plan_matches_a_measured_run_and_ranks_the_large_configs():
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.utils.memory import estimate_memory
+
+    # Llama-2-7B, one GPU, 2048 tokens: 121.2 GiB peak allocated was measured on a B200
+    one = estimate_memory(CONFIGS["llama2-7b"], world=1, seq_len=2048)
+    assert abs(one["total"] / 2**30 - 121.2) < 3.0 and one["buffers"] == 0 and one["fits"]
+    eight = estimate_memory(CONFIGS["llama2-7b"], world=8, seq_len=2048)
+    assert eight["state"] * 8 == one["state"] and eight["buffers"] > 0 and eight["total"] < one["total"] / 3
+    # 70B on 8 GPUs only fits with activation checkpointing... and not at all on 4
+    big = CONFIGS["llama2-70b"]
+    assert estimate_memory(big, 8, 2048, checkpoint_layers=80)["fits"]
+    assert estimate_memory(big, 8, 2048, checkpoint_layers=80)["total"] < estimate_memory(big, 8, 2048)["total"]
+    assert not estimate_memory(big, 4, 2048, checkpoint_layers=80)["fits"]

@@ -147,6 +147,12 @@ def main() -> None:
     args = parse_with_config(ap)
     rank, world, device = init_distributed()
     cfg = CONFIGS[args.model]
+    if rank == 0:
+        from .utils.memory import estimate_memory
+
+        plan = estimate_memory(cfg, world, args.seq_len, args.batch, args.checkpoint_layers)
+        print(json.dumps({"memory_plan_gib": {k: round(v / 2**30, 1) for k, v in plan.items() if k != "fits"},
+                          "fits_b200": bool(plan["fits"])}), flush=True)
     model = build_llama(cfg, device, comm_backend=args.comm_backend, checkpoint_layers=args.checkpoint_layers)
     opt = ShardedAdamW(model, lr=args.lr, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=args.max_grad_norm)
     step = TrainStep(model, opt, device)

@@ -376,6 +376,7 @@ class ParamGroup:
         self._secondary_shard: torch.Tensor | None = None
         self._secondary_valid = False
         self._secondary_backend: CommBackend | None = None
+        self._gathered_from_secondary = False
 
     # ------------------------------------------------------------------ hierarchical partitioning
     def set_secondary_shard_group(self, group: dist.ProcessGroup | None) -> None:
@@ -618,7 +619,7 @@ class ParamGroup:
         assert self.comm_ctx is not None and self.comm_ctx.streams is not None
         self.comm_ctx.streams.wait_event(None, self._ag_event)
         self._ag_event = None
-        if (self.secondary_group is not None and not self._alias_data and not getattr(self, "_gathered_from_secondary", False)
+        if (self.secondary_group is not None and not self._alias_data and not self._gathered_from_secondary
                 and self._training_state == TrainingState.FORWARD and self.reshard_after_forward and torch.is_grad_enabled()
                 and not is_backward_running()):
             self._save_secondary_shard()

@@ -87,3 +87,35 @@ def _optim_roundtrip_worker(rank, world, path):
 @pytest.mark.timeout(300)
 def test_model_and_sharded_adamw_roundtrip(tmp_path):
     run_distributed(_optim_roundtrip_worker, 2, str(tmp_path / "ckpt2"))
+
+
+# ------------------------------------------------------------------------------------------------ damaged checkpoints
+def _load_damaged_worker(rank, world, path, kind):
+    """A checkpoint with a missing shard file, or one written for a model of another size, must fail loudly on every rank
+    instead of loading partial or shifted data."""
+    from yafsdp_b200 import checkpoint
+
+    if kind == "wrong_model":
+        model = _shard(_build(seed=1, d=32))  # twice the width: the saved flat tensors have other sizes
+    else:
+        model = _shard(_build(seed=1))
+    before = {n: p.full_tensor().clone() for n, p in model.named_parameters()}
+    with pytest.raises(BaseException) as err:  # torch's CheckpointException derives from BaseException
+        checkpoint.load(path, model)
+    assert ("flat form" if kind == "wrong_model" else "No such file") in str(err.value)
+    if kind == "wrong_model":
+        # the planner refused before anything was read: the model is untouched
+        for n, p in model.named_parameters():
+            assert torch.equal(p.full_tensor(), before[n]), n
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("kind", ["missing_shard", "wrong_model"])
+def test_damaged_checkpoint_fails_loudly(tmp_path, kind):
+    path = str(tmp_path / "ckpt")
+    run_distributed(_save_worker, 2, path)
+    if kind == "missing_shard":
+        shards = sorted(f for f in os.listdir(path) if f.endswith(".distcp"))
+        assert len(shards) == 2
+        os.remove(os.path.join(path, shards[1]))
+    run_distributed(_load_damaged_worker, 1, path, kind)  # one loading rank: a failing load cannot leave peers waiting

@@ -61,13 +61,71 @@ def _worker(rank, world):
     assert Int8Weight.calls["pre"] == pre + 1 and Int8Weight.calls["post"] > post, (pre, post, Int8Weight.calls, g._is_unsharded, type(lin.weight))
     want_w2 = torch.clamp(torch.round((full + 0.5) / SCALE), -127, 127) * SCALE
     assert torch.allclose(out2, nn.functional.linear(nn.functional.layer_norm(x, (24,)), want_w2), atol=1e-5)
-    # mixing extension and ordinary parameters in one group is refused with a clear message
-    lin2 = nn.Linear(8, 8)
-    lin2.weight = nn.Parameter(lin2.weight.data.as_subclass(Int8Weight))
-    with pytest.raises(AssertionError, match="group of their own"):
-        fully_shard(lin2, mp_policy=policy)
+
+
+def _mixed_worker(rank, world):
+    """Extension and ordinary parameters under ONE fully_shard call: one group per all-gather dtype, side by side in the
+    shared buffers, trained like the unsharded (quantising) model."""
+    from yafsdp_b200 import MixedPrecisionPolicy, fully_shard
+    from yafsdp_b200.group import GroupSet
+    from yafsdp_b200.optim import param_groups_of
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm = nn.LayerNorm(24)
+            self.lin = nn.Linear(24, 24)
+
+        def forward(self, x):
+            return x + self.lin(self.norm(x))
+
+    def build():
+        torch.manual_seed(0)
+        return nn.Sequential(Block(), Block(), nn.Linear(24, 8))
+
+    policy = MixedPrecisionPolicy(all_gather_dtype_to_param_cls={torch.int8: Int8Weight})
+    model = build()
+    for blk in (model[0], model[1]):
+        blk.lin.weight = nn.Parameter(blk.lin.weight.data.as_subclass(Int8Weight))
+        fully_shard(blk, mp_policy=policy)
+    fully_shard(model[2], mp_policy=policy)
+    fully_shard(model, mp_policy=policy)
+    gs = model[0]._get_fsdp_state()._param_group
+    assert isinstance(gs, GroupSet) and [g.all_gather_dtype for g in gs.groups] == [torch.float32, torch.int8]
+    assert len(gs.params) == 4 and len(param_groups_of(model)) == 5
+
+    def quantise(w):
+        return torch.clamp(torch.round(w / SCALE), -127, 127) * SCALE
+
+    ref = build()
+    x_all = [torch.randn(4, 24, generator=torch.Generator().manual_seed(5 + r)) for r in range(world)]
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    for _ in range(3):
+        opt.zero_grad()
+        model(x_all[rank]).pow(2).mean().backward()
+        opt.step()
+        # reference: forward with the quantised weights (straight-through: the gradient goes to the fp32 master)
+        ref_opt.zero_grad()
+        for r in range(world):
+            h = x_all[r]
+            for blk in (ref[0], ref[1]):
+                w = blk.lin.weight + (quantise(blk.lin.weight) - blk.lin.weight).detach()
+                h = h + nn.functional.linear(blk.norm(h), w, blk.lin.bias)
+            (ref[2](h).pow(2).mean() / world).backward()
+        ref_opt.step()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.full_tensor(), q.detach(), atol=1e-5), n
+    # state dict keys and shapes are those of the plain model
+    sd = model.state_dict()
+    assert set(sd) == set(ref.state_dict()) and sd["0.lin.weight"].shape == (24, 24)
 
 
 @pytest.mark.timeout(120)
 def test_all_gather_extension_int8():
     run_distributed(_worker, 2)
+
+
+@pytest.mark.timeout(180)
+def test_extension_and_ordinary_parameters_in_one_module():
+    run_distributed(_mixed_worker, 2)

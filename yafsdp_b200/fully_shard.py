@@ -16,7 +16,7 @@ from torch.distributed.device_mesh import DeviceMesh, init_device_mesh
 
 from .api import MixedPrecisionPolicy
 from .common import ShardMeshInfo
-from .group import ParamGroup
+from .group import GroupSet, ParamGroup
 from .state import FSDPState, get_module_state
 
 __all__ = ["fully_shard", "YaFSDPModule", "UnshardHandle"]
@@ -103,6 +103,23 @@ def _move_states_to_device(params: list[nn.Parameter], buffers: list[torch.Tenso
 
 
 # --------------------------------------------------------------------------------------- entry point
+def _split_by_all_gather_dtype(params: list[nn.Parameter], mp_policy: MixedPrecisionPolicy) -> list[list[nn.Parameter]]:
+    """Parameters whose class is listed in ``all_gather_dtype_to_param_cls`` travel in that dtype: one list per dtype,
+    ordinary parameters first (``ya_fsdp/_param_group.py:194-228``)."""
+    mapping = mp_policy.all_gather_dtype_to_param_cls
+    if not mapping:
+        return [params]
+    buckets: dict[Any, list[nn.Parameter]] = {None: []}
+    for p in params:
+        key = None
+        for dtype, classes in mapping.items():
+            if isinstance(p.data, classes if isinstance(classes, tuple) else (classes,)):
+                key = dtype
+                break
+        buckets.setdefault(key, []).append(p)
+    return [ps for ps in buckets.values() if ps]
+
+
 def fully_shard(
     module: nn.Module | list[nn.Module],
     *,
@@ -149,7 +166,9 @@ def fully_shard(
     params, buffers = _managed_states(managed, ignored_params)
     _move_states_to_device(params, buffers, device)
     if params:
-        state._param_group = ParamGroup(params, modules, mesh_info, reshard, device, mp_policy, shard_alignment)
+        by_class = _split_by_all_gather_dtype(params, mp_policy)
+        groups = [ParamGroup(ps, modules, mesh_info, reshard, device, mp_policy, shard_alignment) for ps in by_class]
+        state._param_group = groups[0] if len(groups) == 1 else GroupSet(groups)  # type: ignore[assignment]
 
     for m in modules:
         cls = m.__class__

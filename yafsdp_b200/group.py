@@ -98,10 +98,10 @@ class BufferContext:
         self.nbytes = nbytes
         self.tensor = backend.alloc(nbytes, torch.uint8, device, "gather_output" if self.kind == "data" else "reduce_input")
 
-    def view(self, dtype: torch.dtype, numel: int) -> torch.Tensor:
+    def view(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
         assert self.tensor is not None
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
-        return self.tensor[:nbytes].view(dtype)
+        return self.tensor[byte_offset : byte_offset + nbytes].view(dtype)
 
     def __repr__(self) -> str:
         return f"BufferContext({self.kind}#{self.index}, {self.nbytes} B)"
@@ -366,6 +366,11 @@ class ParamGroup:
         self._norm_fused_ok = False
         self.modules_to_backward_prefetch: list[Any] = []
         self.modules_to_forward_prefetch: list[Any] = []
+        # who owns a shared buffer while this group uses it: the group itself, or the GroupSet it is part of; and where
+        # this group's bytes start inside the shared buffers (groups of one set lie side by side)
+        self._owner: Any = self
+        self._data_byte_offset = 0
+        self._grad_byte_offset = 0
         # called on the reduce-scatter stream with this rank's freshly reduced flat gradient shard (before it is
         # accumulated into the sharded gradient)
         self.post_reduce_hook: Callable[[torch.Tensor], None] | None = None
@@ -489,13 +494,15 @@ class ParamGroup:
         self._ag_input_fresh = False
         # unsharded parameter storage
         self._alias_data = single
-        data_flat = self._ag_input if self._alias_data else data_ctx.view(self.all_gather_dtype, self.layout.padded_numel)
+        data_flat = self._ag_input if self._alias_data else data_ctx.view(self.all_gather_dtype, self.layout.padded_numel,
+                                                                          self._data_byte_offset)
         # unsharded gradient storage
         self._alias_grad = single and self.reduce_scatter_dtype == self.orig_dtype
         trainable = any(sp.requires_grad for sp in self.params)
         grad_flat = None
         if trainable:
-            grad_flat = self.sharded_grad_flat if self._alias_grad else grad_ctx.view(self.reduce_scatter_dtype, self.layout.padded_numel)
+            grad_flat = self.sharded_grad_flat if self._alias_grad else grad_ctx.view(self.reduce_scatter_dtype, self.layout.padded_numel,
+                                                                                      self._grad_byte_offset)
         self._data_flat = data_flat
         self._grad_flat = grad_flat
         for sp in self.params:
@@ -586,12 +593,12 @@ class ParamGroup:
                 self._unshard_pending = True
                 return
             ctx = self.data_ctx
-            if ctx.owner is not None and ctx.owner is not self:
+            if ctx.owner is not None and ctx.owner is not self._owner:
                 raise RuntimeError(
                     f"Data buffer {ctx.index} is still owned by {ctx.owner._module_fqn!r} while {self._module_fqn!r} "
                     "needs it: two groups that share a buffer are unsharded at the same time"
                 )
-            ctx.owner = self
+            ctx.owner = self._owner
             stream = cc.get_all_gather_stream(async_op, self._training_state)
             if stream is not st.current():
                 # the gather input may have just been produced on the compute stream (first gather after the step)
@@ -681,6 +688,8 @@ class ParamGroup:
 
     def _record_post_forward(self) -> None:
         assert self.comm_ctx is not None
+        if self._owner is not self:
+            return  # the set this group belongs to takes the place in the order
         idx = len(self.comm_ctx.post_forward_order)
         self.comm_ctx.post_forward_order.append(self)
         self._post_forward_indices.append(idx)
@@ -725,7 +734,7 @@ class ParamGroup:
         if target._is_unsharded or target._unshard_pending:
             return
         ctx = target.data_ctx
-        if not target._alias_data and ctx is not None and ctx.owner is not None and ctx.owner is not target:
+        if not target._alias_data and ctx is not None and ctx.owner is not None and ctx.owner is not target._owner:
             return  # the buffer is not free yet: the target gathers itself when its turn comes
         with record_function(target._with_fqn(f"YaFSDP::{pass_type}_prefetch")):
             old = target._training_state
@@ -739,13 +748,13 @@ class ParamGroup:
             return
         assert self.grad_ctx is not None and self.comm_ctx is not None and self.comm_ctx.streams is not None
         ctx = self.grad_ctx
-        if ctx.owner is not None and ctx.owner is not self:
+        if ctx.owner is not None and ctx.owner is not self._owner:
             raise RuntimeError(
                 f"Grad buffer {ctx.index} is still owned by {ctx.owner._module_fqn!r} (gradients kept for accumulation "
                 f"without reduction) while {self._module_fqn!r} needs it; give such groups their own grad buffers"
             )
         self.comm_ctx.streams.wait_event(None, ctx.release_event)
-        ctx.owner = self
+        ctx.owner = self._owner
         self._holds_grad_buffer = True
 
     def post_backward(self) -> None:
@@ -994,3 +1003,112 @@ class RegisterPostBackwardFunction(torch.autograd.Function):
     def backward(ctx: Any, *grads: torch.Tensor) -> Any:  # type: ignore[override]
         ctx.hook()
         return (None,) + grads
+
+
+class GroupSet:
+    """Several :class:`ParamGroup` s of ONE ``fully_shard`` call, driven by the scheduler as one group.
+
+    A module whose parameters are gathered in different dtypes (ordinary parameters in the compute dtype, extension
+    parameters in their own wire dtype, ``MixedPrecisionPolicy.all_gather_dtype_to_param_cls``) gets one flat layout,
+    one shard and one all-gather / reduce-scatter per dtype class (the reference splits a group the same way,
+    ``ya_fsdp/_param_group.py:194-228,577-594``).  The groups of a set lie side by side in the shared rotating buffers,
+    own them together and take one place in the forward order.
+
+    Attribute reads go to the first group (the scheduler's flags are kept equal in all of them), attribute writes and
+    method calls go to every group, in order.
+    """
+
+    _OWN = ("groups", "_post_forward_indices")
+
+    def __init__(self, groups: list[ParamGroup]):
+        object.__setattr__(self, "groups", list(groups))
+        object.__setattr__(self, "_post_forward_indices", [])
+        for g in groups:
+            g._owner = self
+
+    # ---- generic forwarding
+    def __getattr__(self, name: str) -> Any:
+        groups = object.__getattribute__(self, "groups")
+        attr = getattr(groups[0], name)
+        if callable(attr) and getattr(attr, "__self__", None) is groups[0]:
+            def broadcast(*args: Any, **kwargs: Any) -> Any:
+                results = [getattr(g, name)(*args, **kwargs) for g in groups]
+                return results[0]
+
+            return broadcast
+        return attr
+
+    def __setattr__(self, name: str, value: Any) -> None:
+        if name in GroupSet._OWN:
+            object.__setattr__(self, name, value)
+            return
+        for g in self.groups:
+            setattr(g, name, value)
+
+    # ---- what differs from a single group
+    @property
+    def _owner(self) -> "GroupSet":
+        return self
+
+    @property
+    def params(self) -> list[ShardedParam]:
+        return [sp for g in self.groups for sp in g.params]
+
+    @property
+    def _is_unsharded(self) -> bool:
+        return all(g._is_unsharded for g in self.groups)
+
+    @property
+    def _unshard_pending(self) -> bool:
+        return any(g._unshard_pending for g in self.groups)
+
+    def _has_sharded_grads(self) -> bool:
+        return any(g._has_sharded_grads() for g in self.groups)
+
+    @staticmethod
+    def _aligned(nbytes: int) -> int:
+        return (nbytes + 1023) // 1024 * 1024
+
+    def data_buffer_nbytes(self) -> int:
+        return sum(self._aligned(g.data_buffer_nbytes()) for g in self.groups)
+
+    def grad_buffer_nbytes(self) -> int:
+        return sum(self._aligned(g.grad_buffer_nbytes()) for g in self.groups)
+
+    def lazy_init(self, comm_ctx: CommContext, data_ctx: BufferContext, grad_ctx: BufferContext) -> None:
+        d = r = 0
+        for g in self.groups:
+            g._data_byte_offset, g._grad_byte_offset = d, r
+            d += self._aligned(g.data_buffer_nbytes())
+            r += self._aligned(g.grad_buffer_nbytes())
+            g.lazy_init(comm_ctx, data_ctx, grad_ctx)
+
+    # ---- one place in the forward order, one backward prefetch
+    def post_forward(self) -> None:
+        for g in self.groups:
+            g.post_forward()
+        if not is_backward_running():
+            cc = self.groups[0].comm_ctx
+            assert cc is not None
+            self._post_forward_indices.append(len(cc.post_forward_order))
+            cc.post_forward_order.append(self)  # type: ignore[arg-type]
+
+    def pre_backward(self, default_prefetch: bool = True) -> None:
+        for g in self.groups:
+            g.pre_backward(default_prefetch=False)
+        if default_prefetch and self._post_forward_indices:
+            cc = self.groups[0].comm_ctx
+            assert cc is not None
+            target_idx = self._post_forward_indices.pop() - 1
+            if target_idx >= 0:
+                target = cc.post_forward_order[target_idx]
+                if (target._alias_data or target.data_ctx is not self.groups[0].data_ctx) and target.unshard_in_backward:
+                    ParamGroup._prefetch_unshard(target, "backward")
+
+    def finalize_backward(self) -> None:
+        for g in self.groups:
+            g.finalize_backward()
+        self._post_forward_indices.clear()
+
+    def __repr__(self) -> str:
+        return f"GroupSet({', '.join(repr(g) for g in self.groups)})"

@@ -30,8 +30,10 @@ def param_groups_of(module: nn.Module) -> list[ParamGroup]:
     out: list[ParamGroup] = []
     for m in module.modules():
         s = get_module_state(m)
-        if s is not None and s._param_group is not None and s._param_group not in out:
-            out.append(s._param_group)
+        if s is not None and s._param_group is not None:
+            for g in getattr(s._param_group, "groups", [s._param_group]):  # a GroupSet contributes its member groups
+                if not any(g is o for o in out):
+                    out.append(g)
     return out
 
 

@@ -34,7 +34,7 @@ def _unsharded_losses(world: int, steps: int):
 
 
 def _sharded_worker(rank, world, steps, expected, mode):
-    from yafsdp_b200 import MixedPrecisionPolicy, fully_shard
+    from yafsdp_b200 import MixedPrecisionPolicy
     from yafsdp_b200.models.llama import CONFIGS, LlamaForCausalLM, shard_llama
 
     if mode == "meta":

@@ -23,7 +23,6 @@ class Experts(nn.Module):
         return sum(x @ w[e] for e in range(w.shape[0]))
 
 
-def _worker(rank, world):
     import torch.distributed as dist
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.tensor import DTensor, Shard, distribute_tensor

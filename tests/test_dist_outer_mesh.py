@@ -23,7 +23,7 @@ class Experts(nn.Module):
         return sum(x @ w[e] for e in range(w.shape[0]))
 
 
-    import torch.distributed as dist
+def _worker(rank, world):
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.tensor import DTensor, Shard, distribute_tensor
 

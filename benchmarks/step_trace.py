@@ -122,7 +122,7 @@ def main() -> None:
     ap.add_argument("--model", default="llama2-7b", choices=sorted(CONFIGS))
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=2)
-    ap.add_argument("--out", default="gpurun_out")
+    ap.add_argument("--out", default="trace_out")
     args = ap.parse_args()
     if args.analyze:
         print(overlap_report(args.analyze, args.baseline, args.steps))

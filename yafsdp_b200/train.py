@@ -164,6 +164,10 @@ def main() -> None:
         t0 = time.perf_counter()
         loss = step(ids).item()
         dt = time.perf_counter() - t0
+        if device.type == "cuda":
+            from .ops import kernels
+
+            kernels.check_status()  # a device-side wait that ran out (a peer that stopped answering) raises here
         if rank == 0:
             print(json.dumps({"step": i, "loss": round(loss, 4), "iter_time_s": round(dt, 4),
                               "tokens_per_s_per_gpu": round(args.batch * args.seq_len / dt, 1),

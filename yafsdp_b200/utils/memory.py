@@ -11,7 +11,7 @@ allocated (the reference leaves this to trial and error with ``--fsdp_num_layers
 * activations kept for backward by the fused layer (bf16 per token and layer: the layer input, both normalised
   inputs, q/k/v, the attention output, the attention-block output, gate/up and their product), or only the layer input
   for a checkpointed layer (plus one layer's worth while it is recomputed);
-* the fp32 logits (written once, overwritten by their gradient).
+* the bf16 logits (written once, overwritten by their gradient).
 """
 
 from __future__ import annotations
@@ -39,7 +39,7 @@ def estimate_memory(cfg: Any, world: int, seq_len: int, batch: int = 1, checkpoi
     ckpt = max(0, min(checkpoint_layers, n_layers))
     activations = (n_layers - ckpt) * per_layer + ckpt * 2.0 * tokens * d + (per_layer if ckpt else 0.0)
     activations += 2.0 * tokens * d * 3  # embedding output, final norm input and output
-    logits = 4.0 * tokens * v
+    logits = 2.0 * tokens * v
     total = state + buffers + activations + logits
     return {"state": state, "buffers": buffers, "activations": activations, "logits": logits, "total": total,
             "fits": float(total < 0.95 * B200_HBM_BYTES)}

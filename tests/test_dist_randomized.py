@@ -1,0 +1,117 @@
+"""Randomised end-to-end check of the scheduler on CPU/gloo: random depth, widths, frozen parameters, tied embeddings,
+resharding policy, micro-batch count and wrap granularity; sharded training must match the unsharded model."""
+
+import random
+
+import pytest
+import torch
+import torch.nn as nn
+
+from dist_utils import run_distributed
+
+
+class _Block(nn.Module):
+    def __init__(self, d, h, norm):
+        super().__init__()
+        self.norm = nn.LayerNorm(d) if norm else nn.Identity()
+        self.a = nn.Linear(d, h)
+        self.b = nn.Linear(h, d, bias=False)
+
+    def forward(self, x):
+        return x + self.b(torch.tanh(self.a(self.norm(x))))
+
+
+class _Net(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        d = cfg["d"]
+        self.emb = nn.Embedding(cfg["vocab"], d)
+        self.layers = nn.ModuleList([_Block(d, h, n) for h, n in zip(cfg["hidden"], cfg["norms"])])
+        self.norm = nn.LayerNorm(d)
+        self.head = nn.Linear(d, cfg["vocab"], bias=False)
+        if cfg["tie"]:
+            self.head.weight = self.emb.weight
+
+    def forward(self, ids):
+        x = self.emb(ids)
+        for l in self.layers:
+            x = l(x)
+        return self.head(self.norm(x))
+
+
+def _config(seed):
+    rng = random.Random(seed)
+    n = rng.randint(1, 4)
+    return {
+        "d": rng.choice([6, 10, 16]), "vocab": rng.choice([11, 32]), "hidden": [rng.choice([5, 12, 24]) for _ in range(n)],
+        "norms": [rng.random() < 0.5 for _ in range(n)], "tie": rng.random() < 0.3, "micro": rng.randint(1, 2),
+        "reshard": rng.choice([True, None]), "freeze": rng.random() < 0.5, "pair_layers": rng.random() < 0.3,
+        "alignment": rng.choice([1, 8]),
+    }
+
+
+def _build(cfg, seed):
+    torch.manual_seed(seed)
+    model = _Net(cfg)
+    if cfg["freeze"]:
+        rng = random.Random(seed + 1)
+        for l in model.layers:
+            if rng.random() < 0.5:
+                l.a.bias.requires_grad_(False)
+            if rng.random() < 0.3:
+                l.b.weight.requires_grad_(False)
+    return model
+
+
+def _loss(model, ids):
+    out = model(ids)
+    return nn.functional.cross_entropy(out.view(-1, out.shape[-1]), ids.view(-1))
+
+
+def _ids(cfg, rank, micro):
+    return torch.randint(0, cfg["vocab"], (3, 5), generator=torch.Generator().manual_seed(1000 + 10 * rank + micro))
+
+
+def _worker(rank, world, seed):
+    from yafsdp_b200 import fully_shard
+
+    cfg = _config(seed)
+    ref = _build(cfg, seed)
+    ref_opt = torch.optim.SGD([p for p in ref.parameters() if p.requires_grad], lr=0.05)
+    for _ in range(2):
+        ref_opt.zero_grad()
+        for r in range(world):
+            for m in range(cfg["micro"]):
+                (_loss(ref, _ids(cfg, r, m)) / (world * cfg["micro"])).backward()
+        ref_opt.step()
+
+    model = _build(cfg, seed)
+    kw = dict(reshard_after_forward=cfg["reshard"], shard_alignment=cfg["alignment"])
+    if cfg["tie"]:
+        fully_shard([model.emb, model.norm, model.head], **{**kw, "reshard_after_forward": False})
+        model.emb._get_fsdp_state()._param_group.dedicated_buffers = True
+    else:
+        fully_shard(model.emb, **kw)
+    layers = list(model.layers)
+    if cfg["pair_layers"] and len(layers) >= 2:
+        fully_shard(layers[:2], **kw)
+        layers = layers[2:]
+    for l in layers:
+        fully_shard(l, **kw)
+    if not cfg["tie"]:
+        fully_shard([model.norm, model.head], **kw)
+    fully_shard(model, **kw)
+    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.05)
+    for _ in range(2):
+        opt.zero_grad()
+        for m in range(cfg["micro"]):
+            (_loss(model, _ids(cfg, rank, m)) / cfg["micro"]).backward()
+        opt.step()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.full_tensor(), q.detach(), atol=2e-5), (seed, cfg, n)
+
+
+@pytest.mark.timeout(240)
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_random_model_matches_unsharded(seed):
+    run_distributed(_worker, 3, seed)

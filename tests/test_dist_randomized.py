@@ -46,7 +46,8 @@ def _config(seed):
         "d": rng.choice([6, 10, 16]), "vocab": rng.choice([11, 32]), "hidden": [rng.choice([5, 12, 24]) for _ in range(n)],
         "norms": [rng.random() < 0.5 for _ in range(n)], "tie": rng.random() < 0.3, "micro": rng.randint(1, 2),
         "reshard": rng.choice([True, None]), "freeze": rng.random() < 0.5, "pair_layers": rng.random() < 0.3,
-        "alignment": rng.choice([1, 8]),
+        "alignment": rng.choice([1, 8]), "eval_between": rng.random() < 0.4, "checkpoint": rng.random() < 0.4,
+        "explicit_unshard": rng.random() < 0.3, "prefetch": rng.random() < 0.3,
     }
 
 
@@ -101,17 +102,34 @@ def _worker(rank, world, seed):
     if not cfg["tie"]:
         fully_shard([model.norm, model.head], **kw)
     fully_shard(model, **kw)
+    if cfg["checkpoint"]:
+        from yafsdp_b200.utils.checkpointing import checkpoint_module
+
+        for l in list(model.layers)[::2]:
+            checkpoint_module(l)
+    singles = [l for l in layers]
+    if cfg["prefetch"] and len(singles) >= 2:
+        singles[0].set_modules_to_forward_prefetch([singles[1]])
+        singles[-1].set_modules_to_backward_prefetch([singles[-2]])
     opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.05)
-    for _ in range(2):
+    for it in range(2):
         opt.zero_grad()
+        if cfg["explicit_unshard"] and it == 1:
+            handle = model.emb.unshard(async_op=True)  # the first group the forward needs: an early, explicit gather
+            if handle is not None:
+                handle.wait()
         for m in range(cfg["micro"]):
             (_loss(model, _ids(cfg, rank, m)) / cfg["micro"]).backward()
         opt.step()
+        if cfg["eval_between"]:
+            with torch.no_grad():
+                got = model(_ids(cfg, rank, 7))
+            assert torch.isfinite(got).all()
     for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
         assert torch.allclose(p.full_tensor(), q.detach(), atol=2e-5), (seed, cfg, n)
 
 
 @pytest.mark.timeout(240)
-@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5, 6, 7])
 def test_random_model_matches_unsharded(seed):
     run_distributed(_worker, 3, seed)

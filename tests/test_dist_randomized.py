@@ -47,7 +47,7 @@ def _config(seed):
         "norms": [rng.random() < 0.5 for _ in range(n)], "tie": rng.random() < 0.3, "micro": rng.randint(1, 2),
         "reshard": rng.choice([True, None]), "freeze": rng.random() < 0.5, "pair_layers": rng.random() < 0.3,
         "alignment": rng.choice([1, 8]), "eval_between": rng.random() < 0.4, "checkpoint": rng.random() < 0.4,
-        "explicit_unshard": rng.random() < 0.3, "prefetch": rng.random() < 0.3,
+        "explicit_unshard": rng.random() < 0.3, "prefetch": rng.random() < 0.3, "adamw": rng.random() < 0.5,
     }
 
 
@@ -78,12 +78,16 @@ def _worker(rank, world, seed):
 
     cfg = _config(seed)
     ref = _build(cfg, seed)
-    ref_opt = torch.optim.SGD([p for p in ref.parameters() if p.requires_grad], lr=0.05)
+    trainable = [p for p in ref.parameters() if p.requires_grad]
+    ref_opt = (torch.optim.AdamW(trainable, lr=0.01, betas=(0.9, 0.95), weight_decay=0.1) if cfg["adamw"]
+               else torch.optim.SGD(trainable, lr=0.05))
     for _ in range(2):
         ref_opt.zero_grad()
         for r in range(world):
             for m in range(cfg["micro"]):
                 (_loss(ref, _ids(cfg, r, m)) / (world * cfg["micro"])).backward()
+        if cfg["adamw"]:
+            torch.nn.utils.clip_grad_norm_(trainable, 0.5)
         ref_opt.step()
 
     model = _build(cfg, seed)
@@ -111,7 +115,12 @@ def _worker(rank, world, seed):
     if cfg["prefetch"] and len(singles) >= 2:
         singles[0].set_modules_to_forward_prefetch([singles[1]])
         singles[-1].set_modules_to_backward_prefetch([singles[-2]])
-    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.05)
+    if cfg["adamw"]:
+        from yafsdp_b200.optim import ShardedAdamW
+
+        opt = ShardedAdamW(model, lr=0.01, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=0.5)
+    else:
+        opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.05)
     for it in range(2):
         opt.zero_grad()
         if cfg["explicit_unshard"] and it == 1:

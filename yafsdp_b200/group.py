@@ -792,8 +792,10 @@ class ParamGroup:
                         (dsts_add if accumulate else dsts_copy).append((sp.rs_view, g))
                         up.grad = None
                         self._sink_written[sp.index] = True
-                    elif not self._sink_written[sp.index] and sp.requires_grad and not self._alias_grad:
-                        sp.rs_view.zero_()  # unused this step: do not reduce another layer's stale bytes
+                    elif not self._sink_written[sp.index] and not self._alias_grad:
+                        # unused this step, or frozen: do not reduce another layer's stale bytes into the flat gradient
+                        # (flat consumers - fused optimizer, norm over the whole shard - read these positions too)
+                        sp.rs_view.zero_()
                 if not self._alias_grad and self.layout.padded_numel > self.layout.total_numel:
                     # padding tail: never written by any gradient, must not carry another layer's bytes into the reduction
                     self._grad_flat[self.layout.total_numel :].zero_()

@@ -155,11 +155,49 @@ class ShardedAdamW:
             for g in self.groups:
                 g._optim_event = None
 
+    @staticmethod
+    def _segments(g: ParamGroup) -> list[tuple[int, int]] | None:
+        """``None`` when every parameter of which this rank holds a piece has a gradient (the whole flat shard is updated in
+        one launch); otherwise the local ranges of those that have one.  Parameters without a gradient (frozen, or unused
+        in this step) are left alone entirely - no weight decay, no moment decay - as ``torch.optim.AdamW`` does."""
+        segs: list[tuple[int, int]] = []
+        full = True
+        for sp in g.params:
+            pl = sp.placement
+            assert pl is not None
+            if not pl.local_numel:
+                continue
+            if sp.sharded_param is None or sp.sharded_param.grad is None:
+                full = False
+                continue
+            lo, hi = pl.shard_offset, pl.shard_offset + pl.local_numel
+            if segs and segs[-1][1] == lo:
+                segs[-1] = (segs[-1][0], hi)
+            else:
+                segs.append((lo, hi))
+        return None if full else segs
+
     def _update_group(self, i: int, coef: torch.Tensor | None, b1: float, b2: float, max_ctas: int = 0) -> None:
         g = self.groups[i]
         p, grad, m, v = g.master_flat, g.sharded_grad_flat, self.exp_avg[i], self.exp_avg_sq[i]
         ag = g.gather_input
         bf16_out = ag if (ag is not None and ag is not p and ag.dtype == torch.bfloat16) else None
+        segs = self._segments(g)
+        if segs is not None:
+            # some parameters have no gradient: update the others range by range with tensor ops
+            bc1 = 1 - b1 ** self.step_count
+            bc2 = 1 - b2 ** self.step_count
+            for lo, hi in segs:
+                gr = grad[lo:hi].float() * (coef if coef is not None else 1.0)
+                pf = p[lo:hi].float()
+                pf.mul_(1 - self.lr * self.weight_decay)
+                m[lo:hi].mul_(b1).add_(gr, alpha=1 - b1)
+                v[lo:hi].mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                denom = (v[lo:hi].sqrt() / math.sqrt(bc2)).add_(self.eps)
+                pf.addcdiv_(m[lo:hi], denom, value=-self.lr / bc1)
+                p[lo:hi].copy_(pf)
+            g._ag_input_fresh = False
+            return
         if p.is_cuda and p.dtype == torch.float32:
             from .ops import kernels
 

@@ -48,6 +48,7 @@ def _config(seed):
         "reshard": rng.choice([True, None]), "freeze": rng.random() < 0.5, "pair_layers": rng.random() < 0.3,
         "alignment": rng.choice([1, 8]), "eval_between": rng.random() < 0.4, "checkpoint": rng.random() < 0.4,
         "explicit_unshard": rng.random() < 0.3, "prefetch": rng.random() < 0.3, "adamw": rng.random() < 0.5,
+        "wide_compute": rng.random() < 0.3, "nosync": rng.random() < 0.3, "state_dict_roundtrip": rng.random() < 0.3,
     }
 
 
@@ -92,6 +93,12 @@ def _worker(rank, world, seed):
 
     model = _build(cfg, seed)
     kw = dict(reshard_after_forward=cfg["reshard"], shard_alignment=cfg["alignment"])
+    if cfg["wide_compute"]:
+        # compute and reduce in float64: exercises the separate gather input, the casts and a reduce dtype that differs from
+        # the parameters' while staying comparable with the fp32 reference
+        from yafsdp_b200 import MixedPrecisionPolicy
+
+        kw["mp_policy"] = MixedPrecisionPolicy(param_dtype=torch.float64, reduce_dtype=torch.float64, cast_forward_inputs=True)
     if cfg["tie"]:
         fully_shard([model.emb, model.norm, model.head], **{**kw, "reshard_after_forward": False})
         model.emb._get_fsdp_state()._param_group.dedicated_buffers = True
@@ -115,6 +122,9 @@ def _worker(rank, world, seed):
     if cfg["prefetch"] and len(singles) >= 2:
         singles[0].set_modules_to_forward_prefetch([singles[1]])
         singles[-1].set_modules_to_backward_prefetch([singles[-2]])
+    nosync = cfg["nosync"] and cfg["micro"] > 1
+    if nosync:
+        model._get_fsdp_state()._lazy_init(allow_no_grad_reduce=True)
     if cfg["adamw"]:
         from yafsdp_b200.optim import ShardedAdamW
 
@@ -128,8 +138,16 @@ def _worker(rank, world, seed):
             if handle is not None:
                 handle.wait()
         for m in range(cfg["micro"]):
+            if nosync:
+                model.set_requires_gradient_sync(m == cfg["micro"] - 1)
             (_loss(model, _ids(cfg, rank, m)) / cfg["micro"]).backward()
         opt.step()
+        if cfg["state_dict_roundtrip"] and it == 0:
+            sd = {k: v.clone() for k, v in model.state_dict().items()}
+            with torch.no_grad():
+                for q in model.parameters():
+                    q.zero_()
+            model.load_state_dict(sd)
         if cfg["eval_between"]:
             with torch.no_grad():
                 got = model(_ids(cfg, rank, 7))
@@ -139,6 +157,6 @@ def _worker(rank, world, seed):
 
 
 @pytest.mark.timeout(240)
-@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5, 6, 7, 13, 16, 28, 38])
 def test_random_model_matches_unsharded(seed):
     run_distributed(_worker, 3, seed)

@@ -160,3 +160,60 @@ def _worker(rank, world, seed):
 @pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5, 6, 7, 13, 16, 28, 38])
 def test_random_model_matches_unsharded(seed):
     run_distributed(_worker, 3, seed)
+
+
+# ------------------------------------------------------------------------------------------------ class-style wrapper
+def _config_v1(seed):
+    cfg = _config(seed)
+    rng = random.Random(seed + 77)
+    cfg.update(tie=False, freeze=False, zero=rng.choice([1, 2, 3]), gas=rng.randint(1, 2), use_norm_cls=rng.random() < 0.6,
+               hpz=rng.random() < 0.4, clip=rng.random() < 0.5)
+    return cfg
+
+
+def _v1_worker(rank, world, seed):
+    import torch.distributed as dist
+    from yafsdp_b200.compat_v1 import YaFSDP
+
+    cfg = _config_v1(seed)
+    ref = _build(cfg, seed)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    for _ in range(2):
+        ref_opt.zero_grad()
+        for r in range(world):
+            for m in range(cfg["gas"]):
+                (_loss(ref, _ids(cfg, r, m)) / (world * cfg["gas"])).backward()
+        if cfg["clip"]:
+            torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.3)
+        ref_opt.step()
+    model = _build(cfg, seed)
+    intra = None
+    if cfg["hpz"] and world == 4 and cfg["zero"] == 3:
+        for lo in (0, 2):
+            g = dist.new_group([lo, lo + 1])
+            if rank // 2 == lo // 2:
+                intra = g
+    wrapped = YaFSDP(
+        model, zero_stage=cfg["zero"], param_dtype=torch.float32,
+        modules_to_wrap_with_names=[(model.emb, "emb")] + [(l, f"layers.{i}") for i, l in enumerate(model.layers)] + [(model.head, "head")],
+        layer_norm_module_cls=nn.LayerNorm if cfg["use_norm_cls"] else None, gradient_accumulation_steps=cfg["gas"],
+        rogue_layer_norm_modules_with_names={model.norm: "norm"}, comm_backend="torch",
+        hpz_first_layers_num=2 if intra is not None else 0, intra_node_data_parallel_process_group=intra,
+    )
+    opt = torch.optim.SGD(list(wrapped.parameters()), lr=0.05)
+    for _ in range(2):
+        wrapped.zero_grad()
+        for m in range(cfg["gas"]):
+            _loss(wrapped, _ids(cfg, rank, m)).backward()  # the wrapper divides by the accumulation steps itself
+        if cfg["clip"]:
+            wrapped.clip_grad_norm_(0.3)
+        opt.step()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        full = p.full_tensor() if hasattr(p, "full_tensor") else p.detach()
+        assert torch.allclose(full, q.detach(), atol=2e-5), (seed, cfg, n)
+
+
+@pytest.mark.timeout(240)
+@pytest.mark.parametrize("seed,world", [(0, 4), (1, 2), (2, 2), (3, 4), (4, 2), (9, 4)])
+def test_random_v1_wrapper_matches_unsharded(seed, world):
+    run_distributed(_v1_worker, world, seed)

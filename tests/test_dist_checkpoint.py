@@ -119,3 +119,45 @@ def test_damaged_checkpoint_fails_loudly(tmp_path, kind):
         assert len(shards) == 2
         os.remove(os.path.join(path, shards[1]))
     run_distributed(_load_damaged_worker, 1, path, kind)  # one loading rank: a failing load cannot leave peers waiting
+
+
+# ------------------------------------------------------------------------------------------------ resume at another world size
+def _adamw_reference(worlds_per_phase, steps_per_phase):
+    """Unsharded AdamW over the same global batches: phase k uses the data of ``worlds_per_phase[k]`` ranks."""
+    model = _build()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    for world, steps in zip(worlds_per_phase, steps_per_phase):
+        for _ in range(steps):
+            opt.zero_grad()
+            for r in range(world):
+                (_loss(model, _data(r)) / world).backward()
+            opt.step()
+    return {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+def _resume_worker(rank, world, path, phase):
+    from yafsdp_b200 import checkpoint
+    from yafsdp_b200.optim import ShardedAdamW
+
+    model = _shard(_build(seed=0 if phase == 0 else 99))
+    opt = ShardedAdamW(model, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    if phase == 1:
+        extra = checkpoint.load(path, model, opt, extra={"step": 0})
+        assert extra["step"] == 2 and opt.step_count == 2
+    for _ in range(2):
+        opt.zero_grad()
+        _loss(model, _data(rank)).backward()
+        opt.step()
+    if phase == 0:
+        checkpoint.save(path, model, opt, extra={"step": 2})
+    else:
+        want = _adamw_reference([2, 3], [2, 2])
+        for n, p in model.named_parameters():
+            assert torch.allclose(p.full_tensor(), want[n], atol=1e-5), n
+
+
+@pytest.mark.timeout(300)
+def test_training_resumes_at_another_world_size_with_optimizer_state(tmp_path):
+    path = str(tmp_path / "ckpt3")
+    run_distributed(_resume_worker, 2, path, 0)
+    run_distributed(_resume_worker, 3, path, 1)

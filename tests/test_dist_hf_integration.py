@@ -67,3 +67,45 @@ def _worker(rank, world, api, tie):
 @pytest.mark.parametrize("api,tie", [("fully_shard", False), ("fully_shard", True), ("v1", False)])
 def test_hf_causal_lm(api, tie):
     run_distributed(_worker, 2, api, tie)
+
+
+# ------------------------------------------------------------------------------------------------ other decoder layouts
+def _tiny_other(kind):
+    torch.manual_seed(0)
+    if kind == "gpt2":  # tied embeddings, learned position embeddings outside the known parts, Conv1D projections
+        from transformers import GPT2Config, GPT2LMHeadModel
+
+        return GPT2LMHeadModel(GPT2Config(n_embd=32, n_layer=2, n_head=4, vocab_size=64, n_positions=32, resid_pdrop=0.0,
+                                          embd_pdrop=0.0, attn_pdrop=0.0, attn_implementation="eager"))
+    from transformers import GPTNeoXConfig, GPTNeoXForCausalLM  # parallel residual, `gpt_neox.layers`, `embed_out`
+
+    return GPTNeoXForCausalLM(GPTNeoXConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                            vocab_size=64, max_position_embeddings=64, hidden_dropout=0.0, attention_dropout=0.0,
+                                            attn_implementation="eager"))
+
+
+def _other_worker(rank, world, kind):
+    from yafsdp_b200 import MixedPrecisionPolicy
+    from yafsdp_b200.integrations.hf import shard_causal_lm
+
+    ref = _tiny_other(kind)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=5e-2)
+    for _ in range(2):
+        ref_opt.zero_grad()
+        for r in range(world):
+            (ref(input_ids=_ids(r), labels=_ids(r)).loss / world).backward()
+        ref_opt.step()
+    model = shard_causal_lm(_tiny_other(kind), mp_policy=MixedPrecisionPolicy(), num_layers_to_checkpoint=1, comm_backend="torch")
+    opt = torch.optim.SGD(model.parameters(), lr=5e-2)
+    for _ in range(2):
+        opt.zero_grad()
+        model(input_ids=_ids(rank), labels=_ids(rank)).loss.backward()
+        opt.step()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.full_tensor(), q.detach(), atol=2e-5), n
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("kind", ["gpt2", "neox"])
+def test_hf_other_decoder_layouts(kind):
+    run_distributed(_other_worker, 2, kind)

@@ -154,8 +154,14 @@ def shard_causal_lm(
 
     kw: dict[str, Any] = dict(mesh=mesh, mp_policy=mp_policy)
     tail = [m for m in (parts.norm, parts.head) if m is not None]
-    if parts.tied:
-        fully_shard([parts.embed, *tail], reshard_after_forward=False, **kw)
+    # modules outside the known parts that own parameters themselves (e.g. learned position embeddings): they join the
+    # embedding's group, which then keeps buffers of its own because such modules may run anywhere in the forward
+    covered = {id(p) for m in (parts.embed, *parts.layers, *tail) for p in m.parameters()}
+    inside = {id(sub) for m in (parts.embed, *parts.layers, *tail) for sub in m.modules()}
+    extra = [m for m in model.modules()
+             if id(m) not in inside and any(id(p) not in covered for p in m.parameters(recurse=False))]
+    if parts.tied or extra:
+        fully_shard([parts.embed, *extra, *(tail if parts.tied else [])], reshard_after_forward=False, **kw)
         parts.embed._get_fsdp_state()._param_group.dedicated_buffers = True  # type: ignore[attr-defined]
     else:
         fully_shard(parts.embed, **kw)

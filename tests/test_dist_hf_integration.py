@@ -109,3 +109,39 @@ def _other_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["gpt2", "neox"])
 def test_hf_other_decoder_layouts(kind):
     run_distributed(_other_worker, 2, kind)
+
+
+# ------------------------------------------------------------------------------------------------ weights in and out
+def _weights_worker(rank, world):
+    """Hugging Face weights load into the package's sharded Llama by name (full tensors, every rank keeps its slices); the
+    loss matches; the gathered full state dict loads back into a Hugging Face model."""
+    from yafsdp_b200 import MixedPrecisionPolicy, checkpoint
+    from yafsdp_b200.models.llama import LlamaConfig, LlamaForCausalLM, shard_llama
+
+    hf = _tiny()
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=hf.config.rms_norm_eps)
+    with torch.device("meta"):
+        model = LlamaForCausalLM(cfg)
+    shard_llama(model, mp_policy=MixedPrecisionPolicy(), comm_backend="torch")  # fp32 compute: exact comparison
+    model.init_weights(seed=11)  # something else than the Hugging Face weights
+    result = model.load_state_dict(hf.state_dict(), strict=False)
+    assert not result.unexpected_keys and not result.missing_keys, result
+    ids = _ids(rank)
+    loss = model(ids, labels=ids)
+    want = hf(input_ids=ids, labels=ids).loss
+    assert torch.allclose(loss, want, atol=1e-5), (loss.item(), want.item())
+    full = checkpoint.full_state_dict(model)
+    if rank == 0:
+        back = _tiny()
+        with torch.no_grad():
+            for p in back.parameters():
+                p.zero_()
+        back.load_state_dict(full, strict=False)
+        for (n, p), (_, q) in zip(back.named_parameters(), hf.named_parameters()):
+            assert torch.equal(p, q), n
+
+
+@pytest.mark.timeout(300)
+def test_hugging_face_weights_load_into_sharded_llama_and_back():
+    run_distributed(_weights_worker, 2)

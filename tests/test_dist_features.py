@@ -563,3 +563,35 @@ def _v1_model_parallel_worker(rank, world):
 @pytest.mark.timeout(240)
 def test_v1_norm_gradients_summed_over_model_parallel_group():
     run_distributed(_v1_model_parallel_worker, 4)
+
+
+# ------------------------------------------------------------------------------------------------
+def _clip_variants_worker(rank, world):
+    """torch's gradient clipping on sharded gradients for the 1-, 2- and infinity-norm (ranks may hold no element of a
+    parameter) and by value."""
+    for norm_type in (1.0, 2.0, float("inf")):
+        ref = _build()
+        for r in range(world):
+            (_loss(ref, _data(r)) / world).backward()
+        want = torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.05, norm_type=norm_type)
+        model = _shard(_build())
+        _loss(model, _data(rank)).backward()
+        got = torch.nn.utils.clip_grad_norm_(model.parameters(), 0.05, norm_type=norm_type)
+        got = got.full_tensor() if hasattr(got, "full_tensor") else got
+        assert torch.allclose(got, want, rtol=1e-5), (norm_type, got, want)
+        for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+            assert torch.allclose(p.grad.full_tensor(), q.grad, atol=1e-6), (norm_type, n)
+    ref = _build()
+    for r in range(world):
+        (_loss(ref, _data(r)) / world).backward()
+    torch.nn.utils.clip_grad_value_(ref.parameters(), 0.002)
+    model = _shard(_build())
+    _loss(model, _data(rank)).backward()
+    torch.nn.utils.clip_grad_value_(model.parameters(), 0.002)
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.grad.full_tensor(), q.grad, atol=1e-7), n
+
+
+@pytest.mark.timeout(180)
+def test_torch_clipping_variants_on_sharded_grads():
+    run_distributed(_clip_variants_worker, 3)

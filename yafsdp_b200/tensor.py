@@ -401,6 +401,11 @@ def _norm_op(func: Any, args: Any, kwargs: Any, spec: RaggedSpec) -> Any:
 
     largs = tree_map(lambda x: _localize(x, spec), args)
     lkwargs = tree_map(lambda x: _localize(x, spec), kwargs)
+    ord_in = args[1] if len(args) > 1 else kwargs.get("ord", 2)
+    if ord_in == float("inf"):
+        # a rank may hold no element of a parameter (ragged shards); the maximum has no identity on an empty tensor, but
+        # for the maximum of absolute values a single zero stands in for "nothing here"
+        largs = (tree_map(lambda x: x.new_zeros(1) if isinstance(x, torch.Tensor) and x.numel() == 0 else x, largs[0]), *largs[1:])
     out = func(*largs, **lkwargs)
     if func is aten.linalg_vector_norm.default and (len(args) > 2 and args[2] is not None or kwargs.get("dim") is not None):
         raise NotImplementedError("vector_norm over a subset of dimensions of a RaggedShardDTensor")
@@ -409,8 +414,17 @@ def _norm_op(func: Any, args: Any, kwargs: Any, spec: RaggedSpec) -> Any:
     if spec.mesh is None or world == 1:
         return out
 
+    if ord_ == float("inf"):
+        from torch.distributed.tensor import Partial
+
+        placement: Any = Partial("max")  # the norm-partial placement covers finite p only
+    elif ord_ in (float("-inf"), 0):
+        raise NotImplementedError(f"{ord_}-norm of a RaggedShardDTensor")
+    else:
+        placement = _NormPartial(norm_type=ord_)
+
     def wrap(t: torch.Tensor) -> DTensor:
-        return DTensor.from_local(t, spec.mesh, [_NormPartial(norm_type=ord_)], run_check=False)
+        return DTensor.from_local(t, spec.mesh, [placement], run_check=False)
 
     return [wrap(t) for t in out] if isinstance(out, (list, tuple)) else wrap(out)
 

@@ -45,22 +45,22 @@ def _check(model, ref, tag):
         assert torch.allclose(p.full_tensor(), q.detach(), atol=3e-5), (tag, n, (p.full_tensor() - q).abs().max().item())
 
 
-def _optimizer_worker(rank, world, name):
-    cfg, ref, model = _models()
-    ref_opt, opt = OPTIMIZERS[name](list(ref.parameters())), OPTIMIZERS[name](list(model.parameters()))
-    for _ in range(3):
-        ref_opt.zero_grad()
-        opt.zero_grad()
-        _backward_both(cfg, ref, model, rank, world)
-        ref_opt.step()
-        opt.step()
-    _check(model, ref, name)
+def _optimizer_worker(rank, world):
+    for name in sorted(OPTIMIZERS):
+        cfg, ref, model = _models()
+        ref_opt, opt = OPTIMIZERS[name](list(ref.parameters())), OPTIMIZERS[name](list(model.parameters()))
+        for _ in range(3):
+            ref_opt.zero_grad()
+            opt.zero_grad()
+            _backward_both(cfg, ref, model, rank, world)
+            ref_opt.step()
+            opt.step()
+        _check(model, ref, name)
 
 
-@pytest.mark.timeout(180)
-@pytest.mark.parametrize("name", sorted(OPTIMIZERS))
-def test_torch_optimizers(name):
-    run_distributed(_optimizer_worker, 3, name)
+@pytest.mark.timeout(300)
+def test_torch_optimizers():
+    run_distributed(_optimizer_worker, 3)
 
 
 def _flows_worker(rank, world):

@@ -222,3 +222,50 @@ def _v1_worker(rank, world, seed):
 @pytest.mark.parametrize("seeds,world", [((0, 3, 9), 4), ((1, 2, 4), 2)])
 def test_random_v1_wrapper_matches_unsharded(seeds, world):
     run_distributed(_many, world, _v1_worker, seeds, timeout=380.0)
+
+
+# ------------------------------------------------------------------------------------------------ pipeline-style schedules
+def _microbatch_schedule_worker(rank, world, seed):
+    """Hooks that external pipeline schedules use: ``set_is_last_backward``, unreduced accumulation
+    (``set_requires_gradient_sync``) and parameters kept gathered between micro-batches (``set_reshard_after_backward``)."""
+    from yafsdp_b200 import fully_shard
+
+    cfg = _config(seed)
+    cfg.update(tie=False, freeze=False, micro=3)
+    ref = _build(cfg, seed)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    for _ in range(2):
+        ref_opt.zero_grad()
+        for r in range(world):
+            for m in range(3):
+                (_loss(ref, _ids(cfg, r, m)) / (world * 3)).backward()
+        ref_opt.step()
+    for variant in ("plain", "nosync", "keep", "keep+nosync"):
+        model = _build(cfg, seed)
+        kw = dict(reshard_after_forward=False) if "keep" in variant else {}
+        fully_shard(model.emb, **kw)
+        for l in model.layers:
+            fully_shard(l, **kw)
+        fully_shard([model.norm, model.head], **kw)
+        fully_shard(model, **kw)
+        if "nosync" in variant:
+            model._get_fsdp_state()._lazy_init(allow_no_grad_reduce=True)
+        opt = torch.optim.SGD(model.parameters(), lr=0.05)
+        for _ in range(2):
+            opt.zero_grad()
+            for m in range(3):
+                last = m == 2
+                model.set_is_last_backward(last)
+                if "nosync" in variant:
+                    model.set_requires_gradient_sync(last)
+                if "keep" in variant:
+                    model.set_reshard_after_backward(last)
+                (_loss(model, _ids(cfg, rank, m)) / 3).backward()
+            opt.step()
+        for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+            assert torch.allclose(p.full_tensor(), q.detach(), atol=2e-5), (variant, n)
+
+
+@pytest.mark.timeout(300)
+def test_micro_batch_schedule_hooks():
+    run_distributed(_microbatch_schedule_worker, 2, 1, timeout=280.0)

@@ -129,7 +129,7 @@ int launch_rs(PeerPtrs pp, float* dst, long long shard_numel, int rank, int worl
     reduce_scatter_pull_kernel<BF16_WIRE, W><<<n_ctas, 256, 0, st>>>(pp, dst, shard_numel, rank, scale, accumulate, sumsq);  \
     return 0;
     YF_RS_CASE(1) YF_RS_CASE(2) YF_RS_CASE(3) YF_RS_CASE(4) YF_RS_CASE(5) YF_RS_CASE(6) YF_RS_CASE(7) YF_RS_CASE(8)
-    YF_RS_CASE(16)
+    YF_RS_CASE(9) YF_RS_CASE(10) YF_RS_CASE(11) YF_RS_CASE(12) YF_RS_CASE(13) YF_RS_CASE(14) YF_RS_CASE(15) YF_RS_CASE(16)
 #undef YF_RS_CASE
     default:
       return -1;
@@ -233,21 +233,25 @@ __global__ void __launch_bounds__(256) allgather_mc_kernel(const uint4* __restri
   }
 }
 
-// Barrier between GPUs on signal pads.  pad layout: unsigned 64-bit words [slot][MAX_RANKS]; rank k writes
-// `seq` into word [slot][k] of every rank's pad and waits until all words [slot][*] of its own pad have
-// reached `seq`.  Sequence numbers only grow, so pads are never reset.
-__global__ void signal_barrier_kernel(PeerPtrs pads, int rank, int world, int slot, unsigned long long seq, unsigned long long timeout_ns) {
-  const int r = threadIdx.x;
-  if (r >= world) return;
+// Signal pads.  Layout: unsigned 64-bit words [slot][MAX_RANKS] in every rank's pad; rank k owns word [slot][k] of every
+// pad and only ever raises it (atomic max), so sequence numbers are monotonic even when two streams signal the same slot
+// and pads are never reset.
+YF_DEVINL void red_max_release_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// one thread per peer: raise word [slot][rank] of that peer's pad to `seq`
+YF_DEVINL void pad_signal(const PeerPtrs& pads, int r, int rank, int slot, unsigned long long seq) {
   __threadfence_system();
-  unsigned long long* theirs = reinterpret_cast<unsigned long long*>(pads.p[r]) + (size_t)slot * MAX_RANKS + rank;
-  st_release_sys_u64(theirs, seq);
+  red_max_release_sys_u64(reinterpret_cast<unsigned long long*>(pads.p[r]) + (size_t)slot * MAX_RANKS + rank, seq);
+}
+// one thread per peer: wait (bounded) until word [slot][r] of this rank's own pad has reached `seq`
+YF_DEVINL void pad_wait(const PeerPtrs& pads, int r, int rank, int slot, unsigned long long seq, unsigned long long timeout_ns) {
   const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(pads.p[rank]) + (size_t)slot * MAX_RANKS + r;
   const uint64_t t0 = yf_globaltimer();
   for (uint32_t it = 0;; ++it) {
     if (ld_acquire_sys_u64(mine) >= seq) break;
     if ((it & 63u) == 63u) {
-      if (yf_globaltimer() - t0 > timeout_ns) {
+      if (yf_aborted() || yf_globaltimer() - t0 > timeout_ns) {
         yf_raise(YF_ERR_FLAG_TIMEOUT, 300 + slot);
         break;
       }
@@ -255,6 +259,15 @@ __global__ void signal_barrier_kernel(PeerPtrs pads, int rank, int world, int sl
     }
   }
   __threadfence_system();
+}
+// mode bit 0: signal, bit 1: wait.  Both = a barrier between the GPUs' streams; signal alone tells the peers that this
+// rank's stream got here; wait alone blocks this stream until every peer's signal `seq` has arrived.
+__global__ void signal_pad_kernel(PeerPtrs pads, int rank, int world, int slot, unsigned long long seq, unsigned long long timeout_ns,
+                                  int mode) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  if (mode & 1) pad_signal(pads, r, rank, slot, seq);
+  if (mode & 2) pad_wait(pads, r, rank, slot, seq, timeout_ns);
 }
 
 // Wait until word `index` of a local flag array reaches `value` (bounded); and its setter.
@@ -344,12 +357,16 @@ extern "C" int yf_allgather_mc(const void* in, void* mc_out, long long shard_byt
   return -(int)cudaGetLastError();
 }
 
-extern "C" int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream) {
-  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || slot < 0 || seq <= 0) return -1;
-  signal_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(pads, world), rank, world, slot,
-                                                                             (unsigned long long)seq,
-                                                                             (unsigned long long)timeout_ms * 1000000ull);
+extern "C" int yf_signal_pad(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, int mode,
+                             void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || slot < 0 || seq <= 0 || (mode & 3) == 0) return -1;
+  signal_pad_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(pads, world), rank, world, slot, (unsigned long long)seq,
+                                                                         (unsigned long long)timeout_ms * 1000000ull, mode & 3);
   return -(int)cudaGetLastError();
+}
+
+extern "C" int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream) {
+  return yf_signal_pad(pads, rank, world, slot, seq, timeout_ms, 3, stream);
 }
 
 extern "C" int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream) {

@@ -9,6 +9,7 @@
 // the three GEMMs of a linear layer (Y = X W^T, dX = dY W, dW = dY^T X) run without a transpose.
 // The fp32 output mode with accumulate writes weight gradients straight into a flat fp32 gradient
 // buffer (the cast and the micro-batch accumulation of a sharded-data-parallel step).
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -23,12 +24,13 @@ constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 
-template <int BLOCK_N>
+template <int BLOCK_N, int CG>
 struct GemmCfg {
+  static constexpr int B_ROWS = BLOCK_N / CG;  // rows of B (N extent) in one CTA's shared memory
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
-  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int B_BYTES = B_ROWS * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int STAGES = (STAGE_BYTES == 49152) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
   static constexpr int STAGING_BYTES = 2 * 16384;  // two [128 rows x 128 B] epilogue staging blocks for TMA stores
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
@@ -187,38 +189,44 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, uint8_t
   tma_store_wait0();
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, int CG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
-  using Cfg = GemmCfg<BLOCK_N>;
-  if (fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
+  using Cfg = GemmCfg<BLOCK_N, CG>;
+  if (CG == 1 && fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
     extern __shared__ uint8_t comm_smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 1023) & ~uintptr_t(1023));
     gather_comm_role(fa, (long long)args.N * args.K * 2, ring, reinterpret_cast<uint64_t*>(ring + COMM_NBUF * COMM_PIECE));
     return;
   }
-  const int cta = (int)blockIdx.x - fa.n_comm;        // index among the GEMM CTAs
-  const int nctas = (int)gridDim.x - fa.n_comm;
+  // CG == 2: the grid is a sequence of CTA pairs (clusters of two); a pair works on one 256 x BLOCK_N tile, CTA `crank` of
+  // the pair on its rows [crank * 128, +128) with the B rows [crank * BLOCK_N / 2, +BLOCK_N / 2) in its shared memory
+  const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0;
+  const int unit = ((int)blockIdx.x - fa.n_comm) / CG;        // index among the tile workers (CTAs or pairs)
+  const int nunits = ((int)gridDim.x - fa.n_comm) / CG;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int TILE_M = BLOCK_M * CG;
+  constexpr int B_ROWS = Cfg::B_ROWS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * Cfg::STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING_BYTES);
-  uint64_t* full = bars;                 // [STAGES]
+  uint64_t* full = bars;                 // [STAGES]  (pairs: only the leader's are used, both CTAs' loads count there)
   uint64_t* empty = bars + STAGES;       // [STAGES]
   uint64_t* tfull = bars + 2 * STAGES;   // [2]
-  uint64_t* tempty = tfull + 2;          // [2]
+  uint64_t* tempty = tfull + 2;          // [2]       (pairs: only the leader's are used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int M = args.M, N = args.N, K = args.K;
-  const int num_m = (M + BLOCK_M - 1) / BLOCK_M;
+  const int num_m = (M + TILE_M - 1) / TILE_M;
   const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int num_k = (K + BLOCK_K - 1) / BLOCK_K;
   const int num_tiles = num_m * num_n;
-  constexpr int GROUP_M = 16;
+  constexpr int GROUP_M = 16 / CG;  // 2048 rows of A share a column block of B through L2
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
@@ -230,16 +238,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
     }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if (CG == 2) {
+      tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // the peer's barriers and TMEM exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -249,19 +263,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     const int first_m = g * GROUP_M;
     const int gsize = min(GROUP_M, num_m - first_m);
     const int r = t - g * per_group;
-    m0 = (first_m + r % gsize) * BLOCK_M;
+    m0 = (first_m + r % gsize) * TILE_M + (int)crank * BLOCK_M;
     n0 = (r / gsize) * BLOCK_N;
   };
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
-      for (int t = cta; t < num_tiles && alive; t += nctas) {
+      for (int t = unit; t < num_tiles && alive; t += nunits) {
         int m0, n0;
         tile_coords(t, m0, n0);
-        if (fa.n_comm > 0) {
+        if (CG == 1 && fa.n_comm > 0) {
           // gather mode: the rows [n0, n0 + BLOCK_N) of B must have landed in the local layer buffer
           const long long lo = fa.b_byte_off + (long long)n0 * K * 2;
           const long long hi = fa.b_byte_off + (long long)min(n0 + BLOCK_N, N) * K * 2 - 1;
@@ -284,25 +298,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (!alive) break;
           fence_proxy_async_global();  // the chunks were written with generic stores; TMA reads them through the async proxy
         }
+        const int nb = n0 + (int)crank * B_ROWS;  // first B row this CTA holds
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, 10)) { alive = false; break; }
-          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           const int k0 = kb * BLOCK_K;
-          if (!args.a_mn) {
-            tma_load_2d(sa, &tma_a, &full[s], k0, m0);
-          } else {
+          if (CG == 2) {
+            // both CTAs' bytes are counted on the leader's barrier (the thread that issues the MMAs waits there)
+            if (leader) mbar_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+            const uint32_t fb = mapa_shared(smem_u32(&full[s]), 0);
+            if (!args.a_mn) {
+              tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * (BLOCK_K * 128), &tma_a, &full[s], m0 + j * 64, k0);
-          }
-          if (!args.b_mn) {
-            tma_load_2d(sb, &tma_b, &full[s], k0, n0);
-          } else {
+              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d_pair(sa + j * (BLOCK_K * 128), &tma_a, fb, m0 + j * 64, k0);
+            }
+            if (!args.b_mn) {
+              tma_load_2d_pair(sb, &tma_b, fb, k0, nb);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * (BLOCK_K * 128), &tma_b, &full[s], n0 + j * 64, k0);
+              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d_pair(sb + j * (BLOCK_K * 128), &tma_b, fb, nb + j * 64, k0);
+            }
+          } else {
+            mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+            if (!args.a_mn) {
+              tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * (BLOCK_K * 128), &tma_a, &full[s], m0 + j * 64, k0);
+            }
+            if (!args.b_mn) {
+              tma_load_2d(sb, &tma_b, &full[s], k0, nb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d(sb + j * (BLOCK_K * 128), &tma_b, &full[s], nb + j * 64, k0);
+            }
           }
         }
       }
@@ -313,15 +346,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(BLOCK_M, BLOCK_N, args.a_mn, args.b_mn);
+    // ------------------------------------------------------------ MMA issuer (pairs: the leader CTA issues for both)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = umma_idesc_bf16(TILE_M, BLOCK_N, args.a_mn, args.b_mn);
       const uint32_t a_lbo = args.a_mn ? BLOCK_K * 128 : 0, b_lbo = args.b_mn ? BLOCK_K * 128 : 0;
       const uint32_t a_kstep = args.a_mn ? UMMA_K * 128 : UMMA_K * 2, b_kstep = args.b_mn ? UMMA_K * 128 : UMMA_K * 2;
       uint32_t it = 0;
       bool alive = true;
       int lt = 0;
-      for (int t = cta; t < num_tiles && alive; t += nctas, ++lt) {
+      for (int t = unit; t < num_tiles && alive; t += nunits, ++lt) {
         const int acc = lt & 1;
         const uint32_t acc_ph = (lt >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, 20)) { alive = false; break; }
@@ -338,11 +371,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             const uint64_t adesc = umma_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bdesc = umma_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            tc_mma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (CG == 2) tc_mma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (CG == 2) {
+            const uint32_t eb = smem_u32(&empty[s]);
+            tc_commit_pair(mapa_shared(eb, 0));
+            tc_commit_pair(mapa_shared(eb, 1));
+          } else {
+            tc_commit(&empty[s]);
+          }
         }
-        if (alive) tc_commit(&tfull[acc]);
+        if (alive) {
+          if (CG == 2) {
+            const uint32_t tb = smem_u32(&tfull[acc]);
+            tc_commit_pair(mapa_shared(tb, 0));
+            tc_commit_pair(mapa_shared(tb, 1));
+          } else {
+            tc_commit(&tfull[acc]);
+          }
+        }
       }
     }
   } else {
@@ -358,7 +407,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     int lt = 0;
     uint32_t chunk_ctr = 0;
     float ss = 0.f;  // sum of squares of this thread's outputs (rows / columns past the edges are exact zeros)
-    for (int t = cta; t < num_tiles && alive; t += nctas, ++lt) {
+    for (int t = unit; t < num_tiles && alive; t += nunits, ++lt) {
       int m0, n0;
       tile_coords(t, m0, n0);
       const int acc = lt & 1;
@@ -404,9 +453,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             }
           }
         }
-        if (c == n_chunks - 1) {  // accumulator fully read: hand it back to the MMA warp
+        if (c == n_chunks - 1) {  // accumulator fully read: hand it back to the MMA warp (of the leader CTA)
           tc_fence_before();
-          mbar_arrive(&tempty[acc]);
+          __syncwarp();
+          if (lane == 0) {
+            if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+            else mbar_arrive(&tempty[acc]);
+          }
         }
         if (fa.scatter) {
           // GEMM -> reduce-scatter: rows of the staged [128 x 32 fp32] block go to their owners' slots, eight lanes per
@@ -450,38 +503,80 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (CG == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
-template <int BLOCK_N>
+// cudaFuncSetAttribute is per device: remember which devices have the opt-in to large dynamic shared memory
+template <typename KernelT>
+int ensure_smem_optin(KernelT kernel, int bytes, bool (&done)[64]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return -(int)e;
+    done[dev] = true;
+  }
+  return 0;
+}
+
+template <int BLOCK_N, int CG>
 int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
                 cudaStream_t stream) {
-  using Cfg = GemmCfg<BLOCK_N>;
+  using Cfg = GemmCfg<BLOCK_N, CG>;
   const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(A, args.M, args.K, lda, 64, BLOCK_K, 2, 1)
                                     : yf_tensor_map_2d(A, args.K, args.M, lda, BLOCK_K, BLOCK_M, 2, 1);
   const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(B, args.N, args.K, ldb, 64, BLOCK_K, 2, 1)
-                                    : yf_tensor_map_2d(B, args.K, args.N, ldb, BLOCK_K, BLOCK_N, 2, 1);
+                                    : yf_tensor_map_2d(B, args.K, args.N, ldb, BLOCK_K, Cfg::B_ROWS, 2, 1);
   const CUtensorMap* mc = yf_tensor_map_2d(args.C, args.N, args.M, args.ldc, args.out_f32 ? 32 : 64, BLOCK_M, args.out_f32 ? 4 : 2, 1);
   if (!ma || !mb || !mc) return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return -(int)e;
-    attr_set = true;
-  }
-  const int num_tiles = ((args.M + BLOCK_M - 1) / BLOCK_M) * ((args.N + BLOCK_N - 1) / BLOCK_N);
+  static bool optin[64] = {};
+  if (int rc = ensure_smem_optin(gemm_bf16_tcgen05_kernel<BLOCK_N, CG>, Cfg::SMEM_BYTES, optin)) return rc;
+  const int tile_m = BLOCK_M * CG;
+  const int num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
   int sms = yf_num_sms();
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
-  int gemm_ctas = sms - fa.n_comm;
-  if (gemm_ctas < 1) return -1;
-  if (num_tiles < gemm_ctas) gemm_ctas = num_tiles;
-  const int grid = gemm_ctas + fa.n_comm;  // never more CTAs than SMs: the communication CTAs and the GEMM CTAs that wait on them are co-resident
-  gemm_bf16_tcgen05_kernel<BLOCK_N><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(*ma, *mb, *mc, args, fa);
+  int units = (sms - fa.n_comm) / CG;
+  if (units < 1) return -1;
+  if (num_tiles < units) units = num_tiles;
+  // never more CTAs than SMs: the communication CTAs and the GEMM CTAs that wait on them are co-resident
+  const int grid = units * CG + fa.n_comm;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BLOCK_N, CG>, *ma, *mb, *mc, args, fa);
+  if (e != cudaSuccess) return -(int)e;
   return -(int)cudaGetLastError();
+}
+
+// Tile shape for a problem: CTA pairs (256 x 256 tiles, half of B per CTA) whenever both extents fill such a tile; single
+// CTAs with 128 x 256 or 128 x 128 tiles for small or ragged problems.
+int dispatch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
+                  cudaStream_t s) {
+  const int M = args.M, N = args.N;
+  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
+  const bool fused = fa.n_comm > 0 || fa.scatter;
+  static const int force_cg = [] {
+    const char* v = getenv("YAFSDP_GEMM_CTA_GROUP");
+    return v ? atoi(v) : 0;
+  }();
+  const bool pair_ok = !fused && use256 && M >= 256 && (M % 256 == 0 || M % 256 > 128 || M >= 2048);
+  if (pair_ok && force_cg != 1) return launch_gemm<256, 2>(A, B, args, fa, lda, ldb, sm_limit, s);
+  return use256 ? launch_gemm<256, 1>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128, 1>(A, B, args, fa, lda, ldb, sm_limit, s);
 }
 
 }  // namespace
@@ -521,11 +616,10 @@ extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, 
   args.accumulate = accumulate ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // 128x256 tiles unless N is small or the 256-wide tiling wastes more of the last column block
-  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
   FusedArgs fa;
   memset(&fa, 0, sizeof(fa));
   fa.sumsq = sumsq;
-  return use256 ? launch_gemm<256>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, fa, lda, ldb, sm_limit, s);
+  return dispatch_gemm(A, B, args, fa, lda, ldb, sm_limit, s);
 }
 
 // All-gather -> GEMM in one kernel.  C[M,N] = A[M,K] * B[N,K]^T where B (row-major, contiguous, K-major) is a
@@ -571,8 +665,7 @@ extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K
   fa.shard_bytes = shard_bytes;
   fa.b_byte_off = b_byte_off;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
-  return use256 ? launch_gemm<256>(A, B, args, fa, lda, K, 0, s) : launch_gemm<128>(A, B, args, fa, lda, K, 0, s);
+  return dispatch_gemm(A, B, args, fa, lda, K, 0, s);
 }
 
 // GEMM -> reduce-scatter in one kernel.  dW[M,N] = A * B^T in fp32 is not stored locally: each 16-byte piece is
@@ -607,6 +700,5 @@ extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, 
   fa.c_flat_off = c_flat_off;
   fa.shard_numel = shard_numel;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
-  return use256 ? launch_gemm<256>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128>(A, B, args, fa, lda, ldb, sm_limit, s);
+  return dispatch_gemm(A, B, args, fa, lda, ldb, sm_limit, s);
 }

@@ -75,6 +75,9 @@ int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long sha
 int yf_reduce_scatter_mc(const void* mc_in, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate,
                          int bf16_wire, int n_ctas, float* sumsq, void* stream);
 int yf_allgather_mc(const void* in, void* mc_out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
+// Signal pads (sequence-numbered flags in every rank's peer-mapped pad): mode 1 = raise this rank's word of `slot` to `seq`
+// in every pad, mode 2 = wait (bounded) until every rank's word of `slot` in the own pad has reached `seq`, 3 = both.
+int yf_signal_pad(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, int mode, void* stream);
 int yf_signal_barrier(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, void* stream);
 int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream);
 int yf_flag_set(void* flags, long long index, long long value, void* stream);

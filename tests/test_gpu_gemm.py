@@ -13,7 +13,8 @@ def _ref(a, b, a_mn, b_mn):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 256), (384, 640, 192), (200, 328, 136), (2048, 1024, 2048)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 256), (384, 640, 192), (200, 328, 136), (2048, 1024, 2048),
+                                   (448, 1000, 136), (2304, 512, 64), (512, 2304, 4096)])
 def test_gemm_matches_fp32(m, n, k, a_mn, b_mn):
     from yafsdp_b200.ops import kernels
 

@@ -88,8 +88,12 @@ class CommBackend:
         """Called once per iteration after the optimizer refreshed the gather inputs (symmetric backends
         need every peer's shard to be final before anyone pulls it)."""
 
+    def before_write(self, buf: torch.Tensor) -> None:
+        """``buf`` was the input of an earlier ``reduce_scatter`` and is about to be overwritten on the current stream.
+        Backends whose peers read the buffer remotely wait here until all of them are done with it."""
+
     def check(self) -> None:
-        """Raise if a device-side bounded wait ran out since the last call (synchronises)."""
+        """Raise if a device-side bounded wait ran out since the last call."""
 
 
 class TorchBackend(CommBackend):

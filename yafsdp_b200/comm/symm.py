@@ -15,8 +15,8 @@ With the ``mc`` transport the arena is bound to an NVSwitch multicast object (al
 reduce-scatter reads the switch-computed sum of all ranks' copies (``multimem.ld_reduce``), the all-gather
 stores each shard once to the multicast address of the layer buffer (``multimem.st``).
 
-Cross-GPU ordering uses signal pads (sequence-numbered flags in peer memory) with bounded waits; a
-wait that runs out sets the library status word, which ``check()`` reads.
+Cross-GPU ordering uses signal pads (sequence-numbered flags in peer memory, raised with atomic max) with
+bounded waits; a wait that runs out sets the library status word, which ``check()`` reads.
 
 This is the structure the reference gets from its optional closed-source library (registered
 buffers owned by the communication layer, in-place collectives, fp32 accumulation:
@@ -161,12 +161,39 @@ def _ptr_array(ptrs: list[int]) -> ctypes.Array:
 
 
 class SymmBackend(CommBackend):
+    """Peer-memory collectives.  ``ag_transport`` / ``rs_transport`` choose how the bytes move:
+
+    * ``"ce"``: the copy engines (one ``cudaMemcpyAsync`` per peer, spread over a pool of copy streams per collective);
+      the all-gather then takes no SM at all, the reduce-scatter only a local sum over staging slots;
+    * ``"sm"``: the pull kernels load from peer memory themselves;
+    * ``"mc"``: NVSwitch multicast (``multimem``): the switch sums the gradient copies and replicates the parameter
+      shards, so each GPU receives 1/world of the gradient bytes and sends each shard once (needs ``multicast=True``).
+
+    The defaults are per world size (``DEFAULT_TRANSPORTS``); the environment variables ``YAFSDP_AG_TRANSPORT``,
+    ``YAFSDP_RS_TRANSPORT``, ``YAFSDP_SYMM_TRANSPORT`` (both), ``YAFSDP_AG_CTAS``, ``YAFSDP_RS_CTAS`` override the
+    constructor arguments; :meth:`set_transports` switches between steps.
+
+    Ordering between GPUs (all waits bounded, a wait that runs out sets the library status word):
+
+    * all-gather: the gather inputs are final between the step barrier (after the optimizer) and the end of backward, so
+      pulling needs no per-call synchronisation;
+    * reduce-scatter ``s``: every rank signals "my gradients for ``s`` are complete" and waits for all such signals,
+      reduces, then signals "I have read everyone's buffer for ``s``" WITHOUT waiting; the wait for those signals is
+      deferred to :meth:`before_write`, which the owner of a reduce buffer calls right before the buffer is written
+      again (one or two layers of backward later, when the signals have long arrived).
+    """
+
     name = "symm"
     needs_registered_buffers = True
 
     N_SLOTS = 8
+    SLOT_STEP, SLOT_RS_READY, SLOT_RS_DONE, SLOT_SYNC, SLOT_MC_PRE, SLOT_MC_POST = 0, 1, 2, 3, 4, 5
+    #: measured on 8 x B200 (Llama-2-7B step): all-gather on the copy engines at every world size
+    DEFAULT_TRANSPORTS = {"ag": lambda world: "ce", "rs": lambda world: "ce" if world <= 4 else "sm"}
 
-    def __init__(self, device: torch.device, group: dist.ProcessGroup | None):
+    def __init__(self, device: torch.device, group: dist.ProcessGroup | None, *, ag_transport: str | None = None,
+                 rs_transport: str | None = None, multicast: bool | None = None, ag_ctas: int = 0, rs_ctas: int = 0,
+                 single_comm_stream: bool = False, timeout_ms: int | None = None):
         if group is None or device.type != "cuda":
             raise ValueError("the symmetric backend needs a CUDA device and a process group")
         if group.size() > 16:
@@ -175,52 +202,63 @@ class SymmBackend(CommBackend):
         self.group = group
         self.rank = group.rank()
         self.world = group.size()
-        default_transport = "ce" if self.world <= 4 else "sm"
-        want = {os.environ.get(k, "").lower() for k in ("YAFSDP_SYMM_TRANSPORT", "YAFSDP_AG_TRANSPORT", "YAFSDP_RS_TRANSPORT")}
-        self.arena = SymmArena(device, group, chunk_bytes=int(os.environ.get("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20,
-                               multicast="mc" in want)
+        env = os.environ.get
+        both = env("YAFSDP_SYMM_TRANSPORT", "").lower() or None
+        ag = (env("YAFSDP_AG_TRANSPORT", "").lower() or both or ag_transport or self.DEFAULT_TRANSPORTS["ag"](self.world)).lower()
+        rs = (env("YAFSDP_RS_TRANSPORT", "").lower() or both or rs_transport or self.DEFAULT_TRANSPORTS["rs"](self.world)).lower()
+        if multicast is None:
+            multicast = "mc" in (ag, rs) or env("YAFSDP_SYMM_MULTICAST", "0") == "1"
+        self.arena = SymmArena(device, group, chunk_bytes=int(env("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20, multicast=multicast)
         self.pads = self.arena.alloc(self.N_SLOTS * 16 * 8)
         self.has_multicast = bool(self.arena.mc_bases)
         self._pad_ptrs = _ptr_array(self.arena.peer_ptrs(self.pads))
         self._seq = [0] * self.N_SLOTS
-        self.timeout_ms = int(os.environ.get("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
-        # "ce": bulk peer transfers run on the copy engines (one cudaMemcpyAsync per peer) and only the reduction is a
-        # kernel, so communication takes no SM from the GEMMs; "sm": the pull kernels do the transfers
-        # Measured on B200 (Llama-2-7B step, ms): 2 ranks ce 124.5 / sm 134.2; 4 ranks ce (one copy stream per peer) 121.4 /
-        # sm 146.9; 8 ranks sm (one communication stream) 134.7 / ce with one copy stream 168 / ce with one stream per
-        # peer 142.2.  Hence the default: copy engines up to 4 ranks, pull kernels above.
-        # "mc": through NVSwitch multicast (multimem): the switch sums the gradient copies and replicates the parameter
-        # shards, so each GPU receives 1/world of the gradient bytes and sends each shard once; needs a multicast arena
-        self.transport = os.environ.get("YAFSDP_SYMM_TRANSPORT", default_transport).lower()
-        # the two collectives can use different transports: "ce" all-gather writes straight into the layer buffer and
-        # takes no SM; the reduction needs a kernel anyway, which can pull from the peers itself ("sm") or sum
-        # copy-engine-filled staging slots ("ce")
-        self.ag_transport = os.environ.get("YAFSDP_AG_TRANSPORT", self.transport).lower()
-        self.rs_transport = os.environ.get("YAFSDP_RS_TRANSPORT", self.transport).lower()
-        if not self.has_multicast:
-            if "mc" in (self.ag_transport, self.rs_transport) and self.rank == 0:
-                import warnings
-
-                warnings.warn(f"NVSwitch multicast is not available ({getattr(self.arena, 'last_multicast_error', '')}); "
-                              f"using the {default_transport!r} transport", stacklevel=2)
-            self.ag_transport = default_transport if self.ag_transport == "mc" else self.ag_transport
-            self.rs_transport = default_transport if self.rs_transport == "mc" else self.rs_transport
-        # pull kernels of the two collectives would compete for the same SM resources if they ran side by side: keep
-        # all-gathers and reduce-scatters on one stream then (copy-engine transfers do not have that problem)
-        self.prefers_single_comm_stream = self.rs_transport == "sm" and self.ag_transport == "sm"
+        self.timeout_ms = timeout_ms if timeout_ms is not None else int(env("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
+        self.ag_ctas = int(env("YAFSDP_AG_CTAS", str(ag_ctas)))
+        self.rs_ctas = int(env("YAFSDP_RS_CTAS", str(rs_ctas)))
+        self.prefers_single_comm_stream = single_comm_stream or env("YAFSDP_SINGLE_COMM_STREAM", "0") == "1"
         self._staging: torch.Tensor | None = None
-        # copy-engine transfers from different peers go to several streams so that they run on different engines
-        self._ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(int(os.environ.get("YAFSDP_CE_STREAMS", str(max(1, min(self.world - 1, 8))))))]
-        self.ag_ctas = int(os.environ.get("YAFSDP_AG_CTAS", "0"))
-        self.rs_ctas = int(os.environ.get("YAFSDP_RS_CTAS", "0"))
+        # copy-engine transfers from different peers go to several streams so that they run on different engines; each
+        # collective has its own pool, so a prefetch all-gather never queues behind the previous layer's reduction copies
+        n_ce = int(env("YAFSDP_CE_STREAMS", str(max(1, min(self.world - 1, 8)))))
+        self._ag_ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(n_ce)]
+        self._rs_ce_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(n_ce)]
         self._ptr_cache: dict[int, ctypes.Array] = {}
         self._int_ptr_cache: dict[int, list[int]] = {}
+        # reduce buffers that peers may still be reading: data pointer -> sequence number of the reduce-scatter
+        self._unread: dict[int, int] = {}
+        self.ag_transport = self.rs_transport = "ce"
+        self.set_transports(ag, rs, warn=True)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
+    def set_transports(self, ag: str | None = None, rs: str | None = None, *, ag_ctas: int | None = None,
+                       rs_ctas: int | None = None, warn: bool = False) -> None:
+        """Switch transports (between steps, on every rank alike).  ``"mc"`` needs the multicast arena chosen at
+        construction; without it the default transport is used instead."""
+        for kind, want in (("ag", ag), ("rs", rs)):
+            if want is None:
+                continue
+            want = want.lower()
+            if want not in ("ce", "sm", "mc"):
+                raise ValueError(f"unknown transport {want!r} (expected 'ce', 'sm' or 'mc')")
+            if want == "mc" and not self.has_multicast:
+                fallback = self.DEFAULT_TRANSPORTS[kind](self.world)
+                if warn and self.rank == 0:
+                    import warnings
+
+                    warnings.warn(f"NVSwitch multicast is not available ({getattr(self.arena, 'last_multicast_error', 'arena built without it')}); "
+                                  f"using the {fallback!r} transport", stacklevel=3)
+                want = fallback
+            setattr(self, f"{kind}_transport", want)
+        if ag_ctas is not None:
+            self.ag_ctas = ag_ctas
+        if rs_ctas is not None:
+            self.rs_ctas = rs_ctas
+
     # ------------------------------------------------------------------ memory
     def alloc(self, numel: int, dtype: torch.dtype, device: torch.device, kind: str) -> torch.Tensor:
-        if kind == "gather_output" and self.ag_transport != "mc":
+        if kind == "gather_output" and not self.has_multicast:
             return torch.empty(numel, dtype=dtype, device=device)  # only this rank reads or writes it
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         return self.arena.alloc(nbytes)[:nbytes].view(dtype)
@@ -242,22 +280,32 @@ class SymmBackend(CommBackend):
         return ptrs
 
     # ------------------------------------------------------------------ ordering between GPUs
+    def _pad(self, slot: int, seq: int, mode: int) -> None:
+        rc = _native.lib().yf_signal_pad(self._pad_ptrs, self.rank, self.world, slot, seq, self.timeout_ms, mode,
+                                         torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_signal_pad")
+
     def barrier(self, slot: int = 0) -> None:
         """All ranks' current streams meet here (device-side, bounded wait)."""
         self._seq[slot] += 1
-        rc = _native.lib().yf_signal_barrier(self._pad_ptrs, self.rank, self.world, slot, self._seq[slot], self.timeout_ms,
-                                             torch.cuda.current_stream().cuda_stream)
-        kernels._check(rc, "yf_signal_barrier")
+        self._pad(slot, self._seq[slot], 3)
 
     def step_barrier(self) -> None:
-        self.barrier(0)
+        self.barrier(self.SLOT_STEP)
 
-    def _ce_copies(self, copies: list[tuple[int, int, int]]) -> None:
+    def before_write(self, buf: torch.Tensor) -> None:
+        """``buf`` (a reduce input of an earlier :meth:`reduce_scatter`) is about to be overwritten on the current stream:
+        wait until every peer has signalled that it finished reading it."""
+        seq = self._unread.pop(buf.data_ptr(), None)
+        if seq is not None:
+            self._pad(self.SLOT_RS_DONE, seq, 2)
+
+    def _ce_copies(self, copies: list[tuple[int, int, int]], pool: list[torch.cuda.Stream]) -> None:
         """``(dst, src, nbytes)`` device copies, ordered after the work already queued on the current stream and joined
-        back into it; spread over the copy streams when there are several."""
+        back into it; spread over the copy streams of ``pool`` when there are several."""
         lib = _native.lib()
         cur = torch.cuda.current_stream()
-        if len(self._ce_streams) <= 1 or len(copies) <= 1:
+        if len(pool) <= 1 or len(copies) <= 1:
             for d, s, n in copies:
                 rc = lib.yf_memcpy_async(d, s, n, cur.cuda_stream)
                 if rc != 0:
@@ -267,7 +315,7 @@ class SymmBackend(CommBackend):
             start.record(cur)
             used: list[torch.cuda.Stream] = []
             for i, (d, s, n) in enumerate(copies):
-                st = self._ce_streams[i % len(self._ce_streams)]
+                st = pool[i % len(pool)]
                 if st not in used:
                     st.wait_event(start)
                     used.append(st)
@@ -286,19 +334,18 @@ class SymmBackend(CommBackend):
         mc_out = self.arena.mc_ptr(out) if self.ag_transport == "mc" else 0
         if mc_out:
             stream = torch.cuda.current_stream().cuda_stream
-            self.barrier(4)  # every rank is done with what its copy of `out` held before
+            self.barrier(self.SLOT_MC_PRE)  # every rank is done with what its copy of `out` held before
             with torch.autograd._unsafe_preserve_version_counter(out):
                 rc = _native.lib().yf_allgather_mc(inp.data_ptr(), mc_out, nbytes, self.rank, self.world, self.ag_ctas, stream)
             kernels._check(rc, "yf_allgather_mc")
-            self.barrier(5)  # every rank's stores have landed in every copy
+            self.barrier(self.SLOT_MC_POST)  # every rank's stores have landed in every copy
             return
         if self.ag_transport == "ce":
-            lib = _native.lib()
-            stream = torch.cuda.current_stream().cuda_stream
             peers = self._peer_ints(inp)
             base = out.data_ptr()
             with torch.autograd._unsafe_preserve_version_counter(out):
-                self._ce_copies([(base + r * nbytes, peers[r], nbytes) for r in ((self.rank + d) % self.world for d in range(self.world))])
+                self._ce_copies([(base + r * nbytes, peers[r], nbytes) for r in ((self.rank + d) % self.world for d in range(self.world))],
+                                self._ag_ce_streams)
             return
         with torch.autograd._unsafe_preserve_version_counter(out):
             rc = _native.lib().yf_allgather_pull(self._peers(inp), out.data_ptr(), nbytes, self.rank, self.world, self.ag_ctas,
@@ -310,8 +357,12 @@ class SymmBackend(CommBackend):
         if dst.dtype != torch.float32 or inp.dtype not in (torch.float32, torch.bfloat16):
             raise NotImplementedError("the symmetric reduce-scatter produces fp32 from an fp32 or bf16 wire format")
         shard = inp.numel() // self.world
-        self.barrier(1)  # every rank's gradients for this group are complete
+        self.barrier(self.SLOT_RS_READY)  # every rank's gradients for this group are complete
+        seq = self._seq[self.SLOT_RS_READY]
         stream = torch.cuda.current_stream().cuda_stream
+        lib = _native.lib()
+        bf16 = int(inp.dtype == torch.bfloat16)
+        sq = None if sumsq is None else sumsq.data_ptr()
         if self.rs_transport == "ce":
             # copy engines bring every peer's chunk for this rank into local staging slots; a local kernel sums them
             esz = inp.element_size()
@@ -319,7 +370,6 @@ class SymmBackend(CommBackend):
             if self._staging is None or self._staging.numel() < need:
                 self._staging = torch.empty(need, dtype=torch.uint8, device=self.device)
             peers = self._peer_ints(inp)
-            lib = _native.lib()
             sbase = self._staging.data_ptr()
             srcs = []
             copies = []
@@ -329,20 +379,22 @@ class SymmBackend(CommBackend):
                     continue
                 copies.append((sbase + r * shard * esz, peers[r] + self.rank * shard * esz, shard * esz))
                 srcs.append(sbase + r * shard * esz - self.rank * shard * esz)  # the kernel adds rank * shard
-            self._ce_copies(copies)
+            self._ce_copies(copies, self._rs_ce_streams)
+            self._pad(self.SLOT_RS_DONE, seq, 1)  # the peers' buffers have been read: the sum below is local
             rc = lib.yf_reduce_scatter_pull_sumsq(_ptr_array(srcs), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                                  int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
-                                                  None if sumsq is None else sumsq.data_ptr(), stream)
-        elif self.rs_transport == "mc" and self.arena.mc_ptr(inp):
-            rc = _native.lib().yf_reduce_scatter_mc(self.arena.mc_ptr(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                                    int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
-                                                    None if sumsq is None else sumsq.data_ptr(), stream)
+                                                  int(accumulate), bf16, self.rs_ctas, sq, stream)
+            kernels._check(rc, "yf_reduce_scatter_pull")
         else:
-            rc = _native.lib().yf_reduce_scatter_pull_sumsq(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
-                                                            int(accumulate), int(inp.dtype == torch.bfloat16), self.rs_ctas,
-                                                            None if sumsq is None else sumsq.data_ptr(), stream)
-        kernels._check(rc, "yf_reduce_scatter_pull")
-        self.barrier(2)  # every owner has read this rank's buffer: it may be overwritten
+            if self.rs_transport == "mc" and self.arena.mc_ptr(inp):
+                rc = lib.yf_reduce_scatter_mc(self.arena.mc_ptr(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                              int(accumulate), bf16, self.rs_ctas, sq, stream)
+            else:
+                rc = lib.yf_reduce_scatter_pull_sumsq(self._peers(inp), dst.data_ptr(), shard, self.rank, self.world, float(scale),
+                                                      int(accumulate), bf16, self.rs_ctas, sq, stream)
+            kernels._check(rc, "yf_reduce_scatter_pull")
+            self._pad(self.SLOT_RS_DONE, seq, 1)
+        # this rank's buffer may be overwritten once every owner has read it: before_write() waits for that
+        self._unread[inp.data_ptr()] = seq
         return sumsq is not None
 
     def check(self) -> None:

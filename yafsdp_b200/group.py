@@ -118,6 +118,7 @@ class CommContext:
         self.reduce_scatter_stream: Any = None
         self.post_forward_order: list["ParamGroup"] = []
         self.backend: CommBackend = TorchBackend()
+        self.groups: list["ParamGroup"] = []  # every group under the root, in module order (set at the root's lazy init)
 
     def lazy_init(self, device: torch.device, backend: CommBackend | None = None) -> None:
         self.streams = _DeviceStreams(device)
@@ -128,6 +129,20 @@ class CommContext:
             self.reduce_scatter_stream = self.all_gather_stream
         else:
             self.reduce_scatter_stream = self.streams.new_stream(priority=-1)
+
+    def sync_gather_inputs(self, stream: Any) -> None:
+        """Peer-memory backends: peers pull this rank's shards straight out of its gather inputs, so all of them are
+        brought up to date together (not lazily per group) and nobody pulls before every rank has finished writing its
+        own.  Runs on ``stream``; a no-op for backends that exchange data through ``torch.distributed``."""
+        if not self.backend.needs_registered_buffers:
+            return
+        assert self.streams is not None
+        with self.streams.use(stream):
+            for g in self.groups:
+                if g._lazy_inited and not g._alias_data:
+                    g.wait_optimizer()
+                    g._refresh_gather_input()
+            self.backend.step_barrier()
 
     def get_all_gather_stream(self, async_op: bool, training_state: TrainingState) -> Any:
         assert self.streams is not None
@@ -600,10 +615,14 @@ class ParamGroup:
                 )
             ctx.owner = self._owner
             stream = cc.get_all_gather_stream(async_op, self._training_state)
-            if stream is not st.current():
+            stale = not (self._ag_input_fresh and self._ag_input_version == self._master._version)
+            if stream is not st.current() and stale:
                 # the gather input may have just been produced on the compute stream (first gather after the step)
-                if not (self._ag_input_fresh and self._ag_input_version == self._master._version):
-                    st.wait_stream(stream, st.current())
+                st.wait_stream(stream, st.current())
+            if stale and cc.backend.needs_registered_buffers:
+                # a gather outside a root forward (explicit unshard() after an optimizer step): every rank refreshes all of
+                # its gather inputs and the ranks meet before anyone pulls
+                cc.sync_gather_inputs(stream)
             st.wait_event(stream, ctx.release_event)
             with st.use(stream):
                 if (self.secondary_group is not None and self._secondary_valid
@@ -754,6 +773,8 @@ class ParamGroup:
                 f"without reduction) while {self._module_fqn!r} needs it; give such groups their own grad buffers"
             )
         self.comm_ctx.streams.wait_event(None, ctx.release_event)
+        if self._grad_flat is not None:
+            self.comm_ctx.backend.before_write(self._grad_flat)
         ctx.owner = self._owner
         self._holds_grad_buffer = True
 

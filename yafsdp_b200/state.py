@@ -133,14 +133,7 @@ class FSDPState:
                 self._state_ctx.post_optim_event = None
             else:
                 st.wait_stream(self._comm_ctx.all_gather_stream, st.current())
-            if self._comm_ctx.backend.needs_registered_buffers:
-                # peer-memory backends: peers pull this rank's shards, so all of them are brought up to date now
-                # (not lazily per group) and nobody pulls before every rank has finished writing its own
-                with st.use(self._comm_ctx.all_gather_stream):
-                    for s in self._state_ctx.all_states:
-                        if s._param_group is not None:
-                            s._param_group._refresh_gather_input()
-                    self._comm_ctx.backend.step_barrier()
+            self._comm_ctx.sync_gather_inputs(self._comm_ctx.all_gather_stream)
             if self._device.type == "cuda":
                 with record_function("YaFSDP::inputs_to_device"):
                     args, kwargs = tree_map(lambda x: x.to(self._device, non_blocking=True) if isinstance(x, torch.Tensor) and x.device.type == "cpu" else x, (args, kwargs))
@@ -189,6 +182,7 @@ class FSDPState:
             g = state._param_group
             if g is not None:
                 g.lazy_init(self._comm_ctx, g.data_ctx, g.grad_ctx)  # type: ignore[arg-type]
+                self._comm_ctx.groups.extend(getattr(g, "groups", [g]))
 
     def _init_fqns(self) -> None:
         root = self._modules[0]

@@ -306,34 +306,23 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
 
 }  // namespace
 
-// Backward of yf_attn_fwd.  q/k/v/out/dout as in the forward (dout rows do_stride apart, out rows
-// o_stride apart); lse from the forward.  Scratch supplied by the caller: delta [B,Hq,S] fp32 and
-// dq_accum [B*S, Hq*128] fp32 (zeroed here).  Results: dq (rows dq_stride apart), dk/dv (rows
-// dkv_stride apart), all bf16; they may be column blocks of one fused d(QKV) buffer.
-extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
-                           float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv,
-                           long long q_stride, long long kv_stride, long long o_stride, long long do_stride,
-                           long long dq_stride, long long dkv_stride, float scale, int causal, void* stream) {
-  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv)) return -1;
-  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dq_stride % 8) || (dkv_stride % 8)) return -1;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
-       reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dq_accum)) & 15)
-    return -1;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const CUtensorMap* mq = yf_tensor_map_3d(q, (uint64_t)Hq * HD, S, B, q_stride, (uint64_t)S * q_stride, 64, BQ, 1, 2, 1);
-  const CUtensorMap* mk = yf_tensor_map_3d(k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
-  const CUtensorMap* mv = yf_tensor_map_3d(v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
-  const CUtensorMap* md = yf_tensor_map_3d(dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1);
-  if (!mq || !mk || !mv || !md) return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
+// The three launches of one backward pass (delta pre-pass, main kernel, dQ conversion), shared by both entry points.
+// Allocates nothing: the tensor maps come by reference from the caller, the scratch by pointer.
+static int attn_bwd_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md, const void* out,
+                           const void* dout, const float* lse, float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B,
+                           int S, int Hq, int Hkv, long long o_stride, long long do_stride, long long dq_stride,
+                           long long dkv_stride, float scale, int causal, cudaStream_t st) {
+  static bool optin[64] = {};  // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!optin[dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
     if (e != cudaSuccess) return -(int)e;
-    attr_set = true;
+    optin[dev] = true;
   }
+  if (int rc = yf_tu_bind_status()) return rc;
   const long long T = (long long)B * S;
-  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);
+  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);  // must start at zero on every call
   if (e != cudaSuccess) return -(int)e;
   {
     const long long warps = T * Hq;
@@ -355,7 +344,7 @@ extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal ? 1 : 0;
   dim3 grid((S + BKV - 1) / BKV, Hkv, B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(*mq, *mk, *mv, *md, a);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, md, a);
   {
     const long long items = T * (Hq * HD / 8);
     long long blocks = (items + 255) / 256;
@@ -364,6 +353,30 @@ extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const vo
     attn_dq_convert_kernel<<<(int)blocks, 256, 0, st>>>(dq_accum, reinterpret_cast<__nv_bfloat16*>(dq), T, Hq * HD, dq_stride);
   }
   return -(int)cudaGetLastError();
+}
+
+// Backward of yf_attn_fwd.  q/k/v/out/dout as in the forward (dout rows do_stride apart, out rows
+// o_stride apart); lse from the forward.  Scratch supplied by the caller: delta [B,Hq,S] fp32 and
+// dq_accum [B*S, Hq*128] fp32 (zeroed here).  Results: dq (rows dq_stride apart), dk/dv (rows
+// dkv_stride apart), all bf16; they may be column blocks of one fused d(QKV) buffer.
+extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                           float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                           long long q_stride, long long kv_stride, long long o_stride, long long do_stride,
+                           long long dq_stride, long long dkv_stride, float scale, int causal, void* stream) {
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv)) return -1;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8) || (do_stride % 8) || (dq_stride % 8) || (dkv_stride % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
+       reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dq_accum)) & 15)
+    return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const CUtensorMap* mq = yf_tensor_map_3d(q, (uint64_t)Hq * HD, S, B, q_stride, (uint64_t)S * q_stride, 64, BQ, 1, 2, 1);
+  const CUtensorMap* mk = yf_tensor_map_3d(k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
+  const CUtensorMap* mv = yf_tensor_map_3d(v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
+  const CUtensorMap* md = yf_tensor_map_3d(dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1);
+  if (!mq || !mk || !mv || !md) return -2;
+  return attn_bwd_launch(*mq, *mk, *mv, *md, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
+                         dkv_stride, scale, causal, st);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -444,42 +457,6 @@ extern "C" int yf_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
       yf_tensor_map_3d_encode(&mv, v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1) != 0 ||
       yf_tensor_map_3d_encode(&md, dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1) != 0)
     return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
-    if (e != cudaSuccess) return -(int)e;
-    attr_set = true;
-  }
-  const long long T = (long long)B * S;
-  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);  // must start at zero on every call
-  if (e != cudaSuccess) return -(int)e;
-  {
-    const long long warps = T * Hq;
-    long long blocks = (warps * 32 + 255) / 256;
-    const long long cap = (long long)yf_num_sms() * 8;
-    if (blocks > cap) blocks = cap;
-    attn_delta_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
-                                                  reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq, o_stride, do_stride);
-  }
-  BwdArgs a;
-  a.lse = lse;
-  a.delta = delta;
-  a.dq_accum = dq_accum;
-  a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
-  a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
-  a.dkv_stride = dkv_stride;
-  a.S = S; a.B = B; a.Hq = Hq; a.Hkv = Hkv;
-  a.scale = scale;
-  a.scale_log2 = scale * 1.4426950408889634f;
-  a.causal = causal ? 1 : 0;
-  dim3 grid((S + BKV - 1) / BKV, Hkv, B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, md, a);
-  {
-    const long long items = T * (Hq * HD / 8);
-    long long blocks = (items + 255) / 256;
-    const long long cap = (long long)yf_num_sms() * 8;
-    if (blocks > cap) blocks = cap;
-    attn_dq_convert_kernel<<<(int)blocks, 256, 0, st>>>(dq_accum, reinterpret_cast<__nv_bfloat16*>(dq), T, Hq * HD, dq_stride);
-  }
-  return -(int)cudaGetLastError();
+  return attn_bwd_launch(mq, mk, mv, md, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
+                         dkv_stride, scale, causal, st);
 }

@@ -280,12 +280,15 @@ extern "C" int yf_attn_fwd(const void* q, const void* k, const void* v, void* ou
   const CUtensorMap* mk = yf_tensor_map_3d(k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
   const CUtensorMap* mv = yf_tensor_map_3d(v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
   if (!mq || !mk || !mv) return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool optin[64] = {};  // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!optin[dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
     if (e != cudaSuccess) return -(int)e;
-    attr_set = true;
+    optin[dev] = true;
   }
+  if (int rc = yf_tu_bind_status()) return rc;
   FwdArgs a;
   a.out = reinterpret_cast<__nv_bfloat16*>(out);
   a.lse = lse;

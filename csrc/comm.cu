@@ -233,6 +233,21 @@ __global__ void __launch_bounds__(256) allgather_mc_kernel(const uint4* __restri
   }
 }
 
+// Push a contiguous range of the flat layer gradient (fp32, `numel` elements starting at flat position `flat_off`) into the
+// reduce-scatter slots of the ranks that own it: element f goes to peer_grad[f / shard] + rank * shard + f % shard.  A null
+// source pushes zeros.  For the small gradients (norm weights, biases) that no GEMM epilogue produces.
+__global__ void __launch_bounds__(256) push_flat_kernel(const float4* __restrict__ src, long long nvec, long long flat_off, PeerPtrs peer_grad,
+                                                        long long shard_numel, int rank) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const float4 v = src != nullptr ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long f = flat_off + i * 4;
+    const long long o = f / shard_numel;
+    const long long loc = f - o * shard_numel;
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(peer_grad.p[o]) + (long long)rank * shard_numel + loc) = v;
+  }
+}
+
 // Signal pads.  Layout: unsigned 64-bit words [slot][MAX_RANKS] in every rank's pad; rank k owns word [slot][k] of every
 // pad and only ever raises it (atomic max), so sequence numbers are monotonic even when two streams signal the same slot
 // and pads are never reset.
@@ -357,9 +372,25 @@ extern "C" int yf_allgather_mc(const void* in, void* mc_out, long long shard_byt
   return -(int)cudaGetLastError();
 }
 
+extern "C" int yf_push_flat(const float* src, long long numel, long long flat_off, void* const* peer_grad, long long shard_numel, int rank,
+                            int world, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || numel <= 0) return -1;
+  if ((numel % 4) || (flat_off % 4) || (shard_numel % 4) || flat_off < 0 || flat_off + numel > shard_numel * world) return -1;
+  if (reinterpret_cast<uintptr_t>(src) & 15) return -1;
+  for (int r = 0; r < world; ++r)
+    if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;
+  const long long nvec = numel / 4;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 2 * yf_num_sms()) blocks = 2 * yf_num_sms();
+  push_flat_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4*>(src), nvec, flat_off,
+                                                                                   to_peers(peer_grad, world), shard_numel, rank);
+  return -(int)cudaGetLastError();
+}
+
 extern "C" int yf_signal_pad(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, int mode,
                              void* stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || slot < 0 || seq <= 0 || (mode & 3) == 0) return -1;
+  if (int rc = yf_tu_bind_status()) return rc;
   signal_pad_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(pads, world), rank, world, slot, (unsigned long long)seq,
                                                                          (unsigned long long)timeout_ms * 1000000ull, mode & 3);
   return -(int)cudaGetLastError();
@@ -370,6 +401,7 @@ extern "C" int yf_signal_barrier(void* const* pads, int rank, int world, int slo
 }
 
 extern "C" int yf_flag_wait(const void* flags, long long index, long long value, long long timeout_ms, void* stream) {
+  if (int rc = yf_tu_bind_status()) return rc;
   flag_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const unsigned long long*>(flags), index,
                                                                        (unsigned long long)value, (unsigned long long)timeout_ms * 1000000ull);
   return -(int)cudaGetLastError();

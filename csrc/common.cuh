@@ -2,9 +2,12 @@
 // tcgen05 (5th-gen tensor core) wrappers and the device status word.
 //
 // Every spin in this library is bounded: a wait that runs out records a code in the
-// status word, raises the global abort flag (so every other wait in flight gives up on
-// its next slow-path check) and returns; the kernel then unwinds normally (frees TMEM,
-// exits).  The host reads and clears the status word with yf_status_read().
+// status word, raises the abort flag (so every other wait in flight, in any kernel of the
+// library on any GPU of this process, gives up on its next slow-path check) and returns;
+// the kernel then unwinds normally (frees TMEM, exits).  The status word lives in pinned
+// host memory that every GPU maps, so the host reads it with yf_status_read() without
+// synchronising anything.  Once it is non-zero the outputs of the kernels that ran since are
+// undefined.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -21,25 +24,27 @@ enum YfStatus : int {
   YF_ERR_BAD_ARGUMENT = 3,    // a kernel saw an argument it cannot handle
 };
 
-// [0] = first error code, [1] = detail (site id), [2] = global abort flag, [3] = spare
-// One copy per translation unit (no relocatable device code needed); each .cu registers a
-// reader with YF_TU_STATUS() so that yf_status_read() sees all of them.
-static __device__ int g_yf_status[4];
-typedef int (*yf_status_fn)(int* out4, int clear);
-void yf_register_status(yf_status_fn fn);
-#define YF_TU_STATUS()                                                        \
-  static int yf_tu_status(int* out4, int clear) {                             \
-    cudaError_t e = cudaMemcpyFromSymbol(out4, g_yf_status, 4 * sizeof(int)); \
-    if (e != cudaSuccess) return (int)e;                                      \
-    if (clear && (out4[0] != 0 || out4[2] != 0)) {                            \
-      int z[4] = {0, 0, 0, 0};                                                \
-      e = cudaMemcpyToSymbol(g_yf_status, z, 4 * sizeof(int));                \
-    }                                                                         \
-    return (int)e;                                                            \
-  }                                                                           \
-  static struct YfStatusReg {                                                 \
-    YfStatusReg() { yf_register_status(&yf_tu_status); }                      \
-  } yf_status_reg_instance;
+// The status word: int[4] = {first error code, detail (site id), abort flag, spare} in mapped pinned host memory, one
+// per process (runtime.cu owns it).  Every translation unit keeps the device-visible address in a variable of its own
+// (no relocatable device code needed); YF_TU_STATUS() defines yf_tu_bind_status(), which the launchers of kernels that
+// can wait call first: it stores the address on the current device once.
+int* yf_status_word();
+static __device__ int* g_yf_status;
+#define YF_TU_STATUS()                                                                   \
+  static int yf_tu_bind_status() {                                                       \
+    static bool bound[64] = {};                                                          \
+    int dev = 0;                                                                         \
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;           \
+    if (!bound[dev]) {                                                                   \
+      int* w = yf_status_word();                                                         \
+      void* d = nullptr;                                                                 \
+      if (w == nullptr || cudaHostGetDevicePointer(&d, w, 0) != cudaSuccess) return -1;  \
+      cudaError_t e = cudaMemcpyToSymbol(g_yf_status, &d, sizeof(d));                    \
+      if (e != cudaSuccess) return -(int)e;                                              \
+      bound[dev] = true;                                                                 \
+    }                                                                                    \
+    return 0;                                                                            \
+  }
 
 // default wait limit in nanoseconds (2 s); waits on peers and flags pass their own limit
 #define YF_WAIT_NS_DEFAULT 2000000000ull
@@ -50,13 +55,22 @@ YF_DEVINL uint64_t yf_globaltimer() {
   return t;
 }
 
+// plain stores (host memory: no atomics needed, "first failure wins" only has to hold approximately)
 YF_DEVINL void yf_raise(int code, int site) {
-  if (atomicCAS(&g_yf_status[0], 0, code) == 0) g_yf_status[1] = site;
-  atomicExch(&g_yf_status[2], 1);
-  __threadfence();
+  volatile int* w = g_yf_status;
+  if (w == nullptr) return;
+  if (w[0] == 0) {
+    w[1] = site;
+    w[0] = code;
+  }
+  w[2] = 1;
+  __threadfence_system();
 }
 
-YF_DEVINL bool yf_aborted() { return *((volatile int*)&g_yf_status[2]) != 0; }
+YF_DEVINL bool yf_aborted() {
+  volatile int* w = g_yf_status;
+  return w != nullptr && w[2] != 0;
+}
 
 YF_DEVINL uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -6,7 +6,6 @@
 #include "common.cuh"
 #include "yafsdp_b200.h"
 
-YF_TU_STATUS()
 
 namespace {
 

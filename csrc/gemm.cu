@@ -24,15 +24,22 @@ constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 
-template <int BLOCK_N, int CG>
+// MODE_PLAIN: C is stored locally through TMA.  MODE_SCATTER: GEMM -> reduce-scatter, the fp32 rows of C are pushed to the
+// ranks that own them (see FusedArgs).
+constexpr int MODE_PLAIN = 0, MODE_SCATTER = 1;
+constexpr int SCATTER_COLS = 64;                         // columns per pushed row piece: 256 bytes of fp32
+constexpr int SCATTER_PITCH = SCATTER_COLS * 4 + 16;     // row pitch of the staging block (16 B of padding: no bank conflicts)
+
+template <int BLOCK_N, int CG, int MODE = MODE_PLAIN>
 struct GemmCfg {
   static constexpr int B_ROWS = BLOCK_N / CG;  // rows of B (N extent) in one CTA's shared memory
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   static constexpr int B_BYTES = B_ROWS * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (STAGE_BYTES == 49152) ? 4 : 6;
+  static constexpr int STAGES = (MODE == MODE_SCATTER) ? (STAGE_BYTES == 49152 ? 3 : 4) : ((STAGE_BYTES == 49152) ? 4 : 6);
   static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
-  static constexpr int STAGING_BYTES = 2 * 16384;  // two [128 rows x 128 B] epilogue staging blocks for TMA stores
+  // plain: two [128 rows x 128 B] swizzled blocks for TMA stores; scatter: two [128 rows x 256 B (+ padding)] linear blocks
+  static constexpr int STAGING_BYTES = (MODE == MODE_SCATTER) ? 2 * BLOCK_M * SCATTER_PITCH : 2 * 16384;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
 };
 
@@ -189,11 +196,11 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, uint8_t
   tma_store_wait0();
 }
 
-template <int BLOCK_N, int CG>
+template <int BLOCK_N, int CG, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
-  using Cfg = GemmCfg<BLOCK_N, CG>;
+  using Cfg = GemmCfg<BLOCK_N, CG, MODE>;
   if (CG == 1 && fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
     extern __shared__ uint8_t comm_smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -416,11 +423,62 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
       const float alpha = args.alpha;
+      if constexpr (MODE == MODE_SCATTER) {
+        // GEMM -> reduce-scatter.  Every thread owns one row of the accumulator: it moves 64 columns at a time from its
+        // TMEM lane into its own row of a staging block and sends that 256-byte piece with one bulk store (two where the
+        // piece straddles a shard boundary) to the slot that the owning rank keeps for this rank.  No thread touches
+        // another thread's row, so the epilogue needs no block-level barrier; bulk groups are per thread.
+        const int m = m0 + r_in_tile;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / SCATTER_COLS; ++c, ++chunk_ctr) {
+          uint8_t* srow = staging + (chunk_ctr & 1) * (BLOCK_M * SCATTER_PITCH) + r_in_tile * SCATTER_PITCH;
+          tma_store_wait_read1();  // the store that read this row two pieces ago has finished reading
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * SCATTER_COLS + half * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o;
+              o.x = alpha * __uint_as_float(r[4 * j + 0]);
+              o.y = alpha * __uint_as_float(r[4 * j + 1]);
+              o.z = alpha * __uint_as_float(r[4 * j + 2]);
+              o.w = alpha * __uint_as_float(r[4 * j + 3]);
+              *reinterpret_cast<float4*>(srow + half * 128 + j * 16) = o;
+            }
+          }
+          if (c == BLOCK_N / SCATTER_COLS - 1) {  // accumulator fully read: hand it back to the MMA warp (of the leader CTA)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+              else mbar_arrive(&tempty[acc]);
+            }
+          }
+          fence_proxy_async_smem();
+          const int col = n0 + c * SCATTER_COLS;
+          if (m < M && col < N) {
+            const long long ncols = min(SCATTER_COLS, N - col);
+            const long long f = fa.c_flat_off + (long long)m * N + col;   // position in the flat layer gradient
+            const long long o = f / fa.shard_numel;                       // owner rank
+            const long long loc = f - o * fa.shard_numel;
+            const long long first = min(ncols, fa.shard_numel - loc);
+            float* dst = reinterpret_cast<float*>(fa.peer_grad[o]) + (long long)fa.rank * fa.shard_numel + loc;
+            bulk_store(dst, srow, (uint32_t)(first * 4));
+            if (first < ncols) {
+              float* dst2 = reinterpret_cast<float*>(fa.peer_grad[o + 1]) + (long long)fa.rank * fa.shard_numel;
+              bulk_store(dst2, srow + first * 4, (uint32_t)((ncols - first) * 4));
+            }
+          }
+          tma_store_commit();
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < n_chunks; ++c, ++chunk_ctr) {
         uint8_t* stg = staging + (chunk_ctr & 1) * 16384;
         uint8_t* srow = stg + r_in_tile * 128;
-        if (store_thread && !fa.scatter) tma_store_wait_read1();  // the store that last read this block has finished reading
+        if (store_thread) tma_store_wait_read1();  // the store that last read this block has finished reading
         named_bar_sync(1, 128);
         if (args.out_f32) {
           uint32_t r[32];
@@ -461,27 +519,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             else mbar_arrive(&tempty[acc]);
           }
         }
-        if (fa.scatter) {
-          // GEMM -> reduce-scatter: rows of the staged [128 x 32 fp32] block go to their owners' slots, eight lanes per
-          // 128-byte row so that every peer store is a full line
-          named_bar_sync(1, 128);
-          const int et = threadIdx.x - 64;
-#pragma unroll
-          for (int it2 = 0; it2 < 8; ++it2) {
-            const int idx = it2 * 128 + et;
-            const int row = idx >> 3, ch = idx & 7;
-            const int m = m0 + row, col = n0 + c * 32 + ch * 4;
-            if (m < M && col < N) {
-              const float4 v = *reinterpret_cast<const float4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
-              const long long f = fa.c_flat_off + (long long)m * N + col;
-              const long long o = f / fa.shard_numel;
-              const long long loc = f - o * fa.shard_numel;
-              float* dst = reinterpret_cast<float*>(fa.peer_grad[o]) + (long long)fa.rank * fa.shard_numel + loc;
-              *reinterpret_cast<float4*>(dst) = v;
-            }
-          }
-          continue;
-        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (store_thread) {
@@ -493,8 +530,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           tma_store_commit();
         }
       }
+      }
     }
-    if (store_thread && !fa.scatter) tma_store_wait0();
+    if (MODE == MODE_SCATTER || store_thread) tma_store_wait0();  // all of this thread's stores have completed
     if (fa.sumsq != nullptr) {
       ss = warp_sum(ss);
       if (lane == 0) atomicAdd(fa.sumsq, ss);
@@ -524,10 +562,10 @@ int ensure_smem_optin(KernelT kernel, int bytes, bool (&done)[64]) {
   return 0;
 }
 
-template <int BLOCK_N, int CG>
+template <int BLOCK_N, int CG, int MODE = MODE_PLAIN>
 int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
                 cudaStream_t stream) {
-  using Cfg = GemmCfg<BLOCK_N, CG>;
+  using Cfg = GemmCfg<BLOCK_N, CG, MODE>;
   const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(A, args.M, args.K, lda, 64, BLOCK_K, 2, 1)
                                     : yf_tensor_map_2d(A, args.K, args.M, lda, BLOCK_K, BLOCK_M, 2, 1);
   const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(B, args.N, args.K, ldb, 64, BLOCK_K, 2, 1)
@@ -535,7 +573,8 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedA
   const CUtensorMap* mc = yf_tensor_map_2d(args.C, args.N, args.M, args.ldc, args.out_f32 ? 32 : 64, BLOCK_M, args.out_f32 ? 4 : 2, 1);
   if (!ma || !mb || !mc) return -2;
   static bool optin[64] = {};
-  if (int rc = ensure_smem_optin(gemm_bf16_tcgen05_kernel<BLOCK_N, CG>, Cfg::SMEM_BYTES, optin)) return rc;
+  if (int rc = ensure_smem_optin(gemm_bf16_tcgen05_kernel<BLOCK_N, CG, MODE>, Cfg::SMEM_BYTES, optin)) return rc;
+  if (int rc = yf_tu_bind_status()) return rc;
   const int tile_m = BLOCK_M * CG;
   const int num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
   int sms = yf_num_sms();
@@ -558,7 +597,7 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedA
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BLOCK_N, CG>, *ma, *mb, *mc, args, fa);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BLOCK_N, CG, MODE>, *ma, *mb, *mc, args, fa);
   if (e != cudaSuccess) return -(int)e;
   return -(int)cudaGetLastError();
 }
@@ -569,12 +608,17 @@ int dispatch_gemm(const void* A, const void* B, const GemmArgs& args, const Fuse
                   cudaStream_t s) {
   const int M = args.M, N = args.N;
   const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
-  const bool fused = fa.n_comm > 0 || fa.scatter;
+  const bool fused = fa.n_comm > 0;
   static const int force_cg = [] {
     const char* v = getenv("YAFSDP_GEMM_CTA_GROUP");
     return v ? atoi(v) : 0;
   }();
   const bool pair_ok = !fused && use256 && M >= 256 && (M % 256 == 0 || M % 256 > 128 || M >= 2048);
+  if (fa.scatter) {
+    if (pair_ok && force_cg != 1) return launch_gemm<256, 2, MODE_SCATTER>(A, B, args, fa, lda, ldb, sm_limit, s);
+    return use256 ? launch_gemm<256, 1, MODE_SCATTER>(A, B, args, fa, lda, ldb, sm_limit, s)
+                  : launch_gemm<128, 1, MODE_SCATTER>(A, B, args, fa, lda, ldb, sm_limit, s);
+  }
   if (pair_ok && force_cg != 1) return launch_gemm<256, 2>(A, B, args, fa, lda, ldb, sm_limit, s);
   return use256 ? launch_gemm<256, 1>(A, B, args, fa, lda, ldb, sm_limit, s) : launch_gemm<128, 1>(A, B, args, fa, lda, ldb, sm_limit, s);
 }

@@ -48,16 +48,6 @@ std::mutex g_map_mu;
 // values are heap blocks that are never moved or freed: kernels receive them by value, callers by pointer
 std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 
-// function-local statics: the per-file registrars run during static initialisation, possibly before this file's globals
-std::mutex& status_mu() {
-  static std::mutex m;
-  return m;
-}
-std::vector<yf_status_fn>& status_fns() {
-  static std::vector<yf_status_fn> v;
-  return v;
-}
-
 const CUtensorMap* encode(int rank, const void* base, const uint64_t* dims, const uint64_t* pitch_elems,
                           const uint32_t* box, int elem_bytes, int swizzle128) {
   MapKey key;
@@ -149,25 +139,30 @@ int yf_num_sms() {
   return sms[dev];
 }
 
-void yf_register_status(yf_status_fn fn) {
-  std::lock_guard<std::mutex> lk(status_mu());
-  status_fns().push_back(fn);
+// The status word: a page of this library's own static storage, pinned and mapped into every GPU's address space on first
+// use (cudaHostRegister: nothing is allocated, so entry points that promise not to allocate may bind it too).
+int* yf_status_word() {
+  alignas(4096) static int storage[1024];
+  static int* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    memset(storage, 0, sizeof(storage));
+    if (cudaHostRegister(storage, sizeof(storage), cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess) word = storage;
+  });
+  return word;
 }
 
 extern "C" int yf_status_read(int* code, int* site, int clear) {
-  int first = 0, first_site = 0;
-  std::lock_guard<std::mutex> lk(status_mu());
-  for (yf_status_fn fn : status_fns()) {
-    int v[4] = {0, 0, 0, 0};
-    int e = fn(v, clear);
-    if (e != 0) return -e;
-    if (first == 0 && v[0] != 0) {
-      first = v[0];
-      first_site = v[1];
-    }
+  volatile int* w = yf_status_word();
+  if (w == nullptr) return -1;
+  const int c = w[0], s = w[1], aborted = w[2];
+  if (code) *code = (c == 0 && aborted != 0) ? YF_ERR_FLAG_TIMEOUT : c;
+  if (site) *site = s;
+  if (clear && (c != 0 || aborted != 0)) {
+    w[0] = 0;
+    w[1] = 0;
+    w[2] = 0;
   }
-  if (code) *code = first;
-  if (site) *site = first_site;
   return 0;
 }
 

@@ -1,7 +1,7 @@
 // C interface of the native sm_100a library (libyafsdp_b200.so).  Every function launches on the
 // given CUDA stream (a cudaStream_t passed as void*) and returns 0 on success, a negative value on
 // a rejected argument (-1), a tensor-map failure (-2) or a CUDA error (-cudaError_t).  Nothing here
-// synchronises the device except yf_status_read().  Python binds these symbols through ctypes.
+// synchronises the device.  Python binds these symbols through ctypes.
 #pragma once
 #ifdef __cplusplus
 extern "C" {
@@ -9,7 +9,9 @@ extern "C" {
 
 int yf_version(void);
 int yf_sm_count(void);
-// First error recorded by any kernel since the last clearing read (0 = none); synchronous.
+// First error recorded by any kernel of the library, on any GPU of this process, since the last clearing read (0 = none).
+// The status word sits in host memory: the call neither synchronises nor touches a GPU, so it is cheap enough to poll
+// every step.  It reports what kernels have written so far; synchronise first to cover work still in flight.
 int yf_status_read(int* code, int* site, int clear);
 
 // ---- tcgen05 GEMM family (gemm.cu)
@@ -75,6 +77,10 @@ int yf_reduce_scatter_pull_sumsq(void* const* peer_in, float* dst, long long sha
 int yf_reduce_scatter_mc(const void* mc_in, float* dst, long long shard_numel, int rank, int world, float scale, int accumulate,
                          int bf16_wire, int n_ctas, float* sumsq, void* stream);
 int yf_allgather_mc(const void* in, void* mc_out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
+// Push fp32 values of the flat layer gradient into the owners' reduce-scatter slots (companion of yf_gemm_bf16_scatter for
+// gradients that no GEMM produces); src may be null (zeros).  numel, flat_off and shard_numel must be multiples of 4.
+int yf_push_flat(const float* src, long long numel, long long flat_off, void* const* peer_grad, long long shard_numel, int rank,
+                 int world, void* stream);
 // Signal pads (sequence-numbered flags in every rank's peer-mapped pad): mode 1 = raise this rank's word of `slot` to `seq`
 // in every pad, mode 2 = wait (bounded) until every rank's word of `slot` in the own pad has reached `seq`, 3 = both.
 int yf_signal_pad(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, int mode, void* stream);

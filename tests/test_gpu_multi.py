@@ -202,3 +202,72 @@ def _fused_worker(rank, world):
 
 def test_fused_gather_gemm_and_gemm_scatter():
     _run(_fused_worker, _world())
+
+
+def _unshard_after_step_worker(rank, world):
+    """An explicit unshard() after an optimizer step (outside any forward) must gather the UPDATED weights of every
+    rank: the peer-memory backend refreshes all gather inputs and lets the ranks meet before anybody pulls."""
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.ops import kernels
+    from yafsdp_b200.train import build_llama
+
+    dev = torch.device("cuda", rank)
+    cfg = CONFIGS["tiny-gpu"]
+    model = build_llama(cfg, dev, comm_backend="symm")
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)  # a stock optimizer: the gather inputs go stale after its step
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
+    for _ in range(2):
+        opt.zero_grad()
+        model(ids, labels=ids).backward()
+        opt.step()
+        layer = model.model.layers[0]
+        want = {n: p.full_tensor().to(torch.bfloat16) for n, p in layer.named_parameters()}
+        layer.unshard()
+        for n, p in layer.named_parameters():
+            assert torch.equal(p.detach(), want[n]), f"{n}: gathered weights are not the updated ones"
+        layer.reshard()
+    torch.cuda.synchronize()
+    kernels.check_status()
+
+
+def test_unshard_after_optimizer_step_sees_updated_weights():
+    _run(_unshard_after_step_worker, _world())
+
+
+def _train_fused_reduce_worker(rank, world):
+    """Training with the gradient reduce-scatter fused into the weight-gradient GEMMs (rows pushed from the epilogue to
+    their owners) against the NCCL backend, including two micro-batches per step."""
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.ops import kernels
+    from yafsdp_b200.optim import ShardedAdamW
+    from yafsdp_b200.train import build_llama
+
+    dev = torch.device("cuda", rank)
+    cfg = CONFIGS["tiny-gpu"]
+    gen = torch.Generator().manual_seed(1 + rank)
+    batches = [torch.randint(0, cfg.vocab_size, (2, 256), generator=gen).to(dev) for _ in range(2)]
+    losses = {}
+    for name, kw in (("torch", dict(comm_backend="torch")), ("fused", dict(comm_backend="symm", fused_reduce=True))):
+        model = build_llama(cfg, dev, **kw)
+        opt = ShardedAdamW(model, lr=1e-3, max_grad_norm=1.0)
+        out = []
+        for _ in range(4):
+            opt.zero_grad()
+            for ids in batches:  # two micro-batches, each reduced and accumulated into the sharded gradient
+                loss = model(ids, labels=ids)
+                (loss / len(batches)).backward()
+            opt.step()
+            out.append((loss.item(), opt.last_grad_norm.item()))
+        losses[name] = out
+        kernels.check_status()
+        if name == "fused":
+            g = model.model.layers[0]._get_fsdp_state()._param_group
+            assert g.fused_reduce and g._push_ptrs is not None, "the fused path was not active"
+    for (a, na), (b, nb) in zip(losses["torch"], losses["fused"]):
+        assert abs(a - b) < 2e-2 * abs(a), losses
+        assert abs(na - nb) < 3e-2 * abs(na), losses
+    assert losses["fused"][-1][0] < losses["fused"][0][0]
+
+
+def test_training_with_fused_gemm_reduce_scatter():
+    _run(_train_fused_reduce_worker, _world())

@@ -105,6 +105,11 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+def loaded() -> bool:
+    """True once :func:`lib` has loaded the library in this process."""
+    return _lib is not None
+
+
 def lib() -> ctypes.CDLL:
     """The loaded native library.  Builds it first when it is missing and ``nvcc`` is present."""
     global _lib
@@ -153,6 +158,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_add_bf16": [_P, _P, _P, _L, _P],
         "yf_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _F, _I, _P],
         "yf_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
+        "yf_attn_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_gemm_bf16_sumsq": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _F, _I, _P, _P],
         "yf_gemm_bf16_gathered": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _P, _L, _L, _I, _I, _P, ctypes.c_uint, _L, _I, _P],
         "yf_gemm_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _F, _P, _L, _L, _I, _I, _I, _P],
@@ -162,6 +168,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_reduce_scatter_mc": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P, _P],
         "yf_allgather_mc": [_P, _P, _L, _I, _I, _I, _P],
         "yf_signal_barrier": [_P, _I, _I, _I, _L, _L, _P],
+        "yf_signal_pad": [_P, _I, _I, _I, _L, _L, _I, _P],
+        "yf_push_flat": [_P, _L, _L, _P, _L, _I, _I, _P],
         "yf_flag_wait": [_P, _L, _L, _L, _P],
         "yf_flag_set": [_P, _L, _L, _P],
         "yf_memcpy_async": [_P, _P, _L, _P],
@@ -176,3 +184,12 @@ def _declare(l: ctypes.CDLL) -> None:
             continue
         fn.argtypes = args
         fn.restype = _I
+    # a symbol without a declared signature would be called with C-int arguments and truncate pointers: refuse it loudly
+    import re
+
+    header = (_CSRC / "yafsdp_b200.h")
+    if header.exists():
+        exported = set(re.findall(r"^int (yf_\w+)\(", header.read_text(), flags=re.M))
+        missing = sorted(exported - set(sigs))
+        if missing:
+            raise RuntimeError(f"native functions without a ctypes signature in _native._declare: {missing}")

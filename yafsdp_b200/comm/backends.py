@@ -142,8 +142,9 @@ class TorchBackend(CommBackend):
         return False
 
 
-def make_backend(name: str | None, device: torch.device, group: dist.ProcessGroup | None) -> CommBackend:
-    """``"torch"`` (default), ``"symm"`` (peer-memory kernels; CUDA, one node) or ``"auto"``."""
+def make_backend(name: str | None, device: torch.device, group: dist.ProcessGroup | None, **options: object) -> CommBackend:
+    """``"torch"`` (default), ``"symm"`` (peer-memory kernels; CUDA, one node) or ``"auto"``.  ``options`` are the
+    peer-memory backend's constructor arguments (transports, multicast, CTA counts); the NCCL backend has none."""
     name = (name or "torch").lower()
     if name == "auto":
         name = "symm" if device.type == "cuda" and group is not None and 1 < group.size() <= 16 else "torch"
@@ -152,5 +153,5 @@ def make_backend(name: str | None, device: torch.device, group: dist.ProcessGrou
     if name == "symm":
         from .symm import SymmBackend
 
-        return SymmBackend(device, group)
+        return SymmBackend(device, group, **options)  # type: ignore[arg-type]
     raise ValueError(f"unknown comm backend {name!r}")

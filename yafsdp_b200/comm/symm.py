@@ -397,5 +397,34 @@ class SymmBackend(CommBackend):
         self._unread[inp.data_ptr()] = seq
         return sumsq is not None
 
+    def peer_pointers(self, t: torch.Tensor) -> ctypes.Array:
+        """Every rank's address of ``t`` (a tensor of the arena), as the native kernels take them."""
+        return self._peers(t)
+
+    def reduce_pushed(self, dst: torch.Tensor, slots: torch.Tensor, *, scale: float, accumulate: bool,
+                      sumsq: torch.Tensor | None = None, valid_numel: int | None = None) -> bool:
+        """Second half of the fused GEMM -> reduce-scatter: ``slots`` (this rank's reduce buffer, read as ``world`` slots of
+        one shard each) holds what every rank pushed for this rank's shard; wait until all pushes have landed, then
+        ``dst (+)= scale * sum of the slots`` in rank order (fp32, deterministic), optionally with the squared norm.
+        Positions of the flat gradient at or beyond ``valid_numel`` (the layout's padding) are zeroed first."""
+        if dst.dtype != torch.float32 or slots.dtype != torch.float32:
+            raise NotImplementedError("pushed gradients are fp32")
+        shard = slots.numel() // self.world
+        self.barrier(self.SLOT_RS_READY)  # every rank's pushes for this group have completed
+        seq = self._seq[self.SLOT_RS_READY]
+        if valid_numel is not None:
+            lo = max(0, min(shard, valid_numel - self.rank * shard))
+            if lo < shard:
+                slots.view(self.world, shard)[:, lo:].zero_()  # nobody pushes the padding
+        base = slots.data_ptr()
+        srcs = _ptr_array([base + (r - self.rank) * shard * 4 for r in range(self.world)])  # the kernel adds rank * shard
+        rc = _native.lib().yf_reduce_scatter_pull_sumsq(srcs, dst.data_ptr(), shard, self.rank, self.world, float(scale), int(accumulate),
+                                                        0, self.rs_ctas, None if sumsq is None else sumsq.data_ptr(),
+                                                        torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_reduce_scatter_pull")
+        self._pad(self.SLOT_RS_DONE, seq, 1)  # peers may push into these slots again (before_write() waits for this)
+        self._unread[slots.data_ptr()] = seq
+        return sumsq is not None
+
     def check(self) -> None:
         kernels.check_status()

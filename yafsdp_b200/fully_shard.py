@@ -310,6 +310,16 @@ class YaFSDPModule:
         if (g := self._get_fsdp_state()._param_group) is not None:
             g.post_reduce_hook = hook
 
+    def set_fused_gradient_reduce(self, enable: bool = True, *, recurse: bool = True) -> None:
+        """Fuse the gradient reduce-scatter into the weight-gradient GEMMs (peer-memory backend, fp32 reduction): the GEMM
+        epilogue pushes each fp32 row of dW over NVLink into the slot that the owning rank keeps for this rank, and the
+        owner sums its slots locally.  Replaces copy-into-buffer + reduce-scatter + divide + accumulate
+        (``ya_fsdp/_param_group.py:655-771``, ``ya_fsdp/_collectives.py:93-218``).  For groups whose every parameter gets
+        exactly one gradient per backward pass (no weight used twice); other backends ignore the flag."""
+        for state in self._states(recurse):
+            if state._param_group is not None:
+                state._param_group.fused_reduce = enable
+
     def set_secondary_shard_group(self, group: Any, *, recurse: bool = False) -> None:
         """Hierarchical partitioning for this module's parameter group: gather the weights for backward inside ``group``
         (e.g. the ranks of one node) from a secondary shard saved after the forward all-gather."""
@@ -317,13 +327,16 @@ class YaFSDPModule:
             if state._param_group is not None:
                 state._param_group.set_secondary_shard_group(group)
 
-    def set_comm_backend(self, name: str, *, num_grad_buffers: int | None = None) -> None:
-        """Root only, before the first forward: ``"torch"`` (NCCL / gloo), ``"symm"`` (peer-memory kernels)
-        or ``"auto"``; optionally the number of rotating gradient buffers."""
+    def set_comm_backend(self, name: Any, *, num_grad_buffers: int | None = None, **backend_options: Any) -> None:
+        """Root only, before the first forward: ``"torch"`` (NCCL / gloo), ``"symm"`` (peer-memory kernels),
+        ``"auto"``, or a ready :class:`~yafsdp_b200.comm.backends.CommBackend` instance; optionally the number of rotating
+        gradient buffers.  ``backend_options`` go to the backend's constructor, e.g. ``ag_transport="ce"``,
+        ``rs_transport="sm"``, ``multicast=True`` for the peer-memory backend."""
         state = self._get_fsdp_state()
         if state._is_root is not None:
             raise RuntimeError("set_comm_backend must be called before the first forward")
         state._backend_name = name
+        state._backend_options = dict(backend_options)
         state._num_grad_buffers = num_grad_buffers
 
     def _apply(self, *args: Any, **kwargs: Any) -> Any:

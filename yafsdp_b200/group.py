@@ -178,16 +178,49 @@ class GradSink:
             return None
         return g._norm_sq
 
+    def would_accumulate(self) -> bool:
+        """True when the next write adds to a value that is already there: an earlier write of this backward pass, or
+        (single rank, where the sink is the persistent sharded gradient itself) the sum of earlier micro-batches."""
+        g = self.group
+        if g._sink_written[self.index]:
+            return True
+        if g._alias_grad:
+            sp = g.params[self.index].sharded_param
+            return sp is not None and sp.grad is not None
+        return False
+
+    # ---- fused gradient reduction: the producing kernel pushes the gradient to the ranks that own it
+    def pushes(self) -> bool:
+        """True when this backward pass sends the group's gradients straight to their owners' reduce-scatter slots
+        (``ParamGroup.fused_reduce``) instead of writing them into the local flat buffer."""
+        return self.group._push_mode()
+
+    def begin_push(self) -> tuple[Any, int, int, int, int]:
+        """Claim the reduce buffers for a pushed write of the whole parameter; returns what the pushing kernel needs:
+        ``(peer buffer pointers, flat offset of the parameter, shard size, rank, world)``."""
+        g = self.group
+        g._acquire_grad_buffer()
+        if g._sink_written[self.index]:
+            raise RuntimeError(
+                f"parameter {g.params[self.index].fqn!r} receives a second gradient in one backward pass: pushed gradients "
+                "cannot accumulate at the owner; disable fused_reduce for this group")
+        g._sink_counts[self.index] += 1
+        g._sink_written[self.index] = True
+        g._pushed = True
+        return g._push_ptrs, g.layout.flat_offsets[self.index], g.layout.shard_numel, g.rank, g.world_size
+
+    def push_from(self, grad: torch.Tensor | None) -> None:
+        """Push a complete fp32 gradient of this parameter (``None``: zeros) that some other kernel produced."""
+        from .ops import kernels
+
+        ptrs, off, shard, rank, world = self.begin_push()
+        kernels.push_flat(None if grad is None else grad.reshape(-1), self.group.params[self.index].numel, off, ptrs, shard, rank, world)
+
     def begin(self, zero: bool = False) -> tuple[torch.Tensor, bool]:
         g = self.group
         g._acquire_grad_buffer()
         g._sink_counts[self.index] += 1
-        accumulate = g._sink_written[self.index]
-        if not accumulate and g._alias_grad:
-            # single rank: the sink is the persistent sharded gradient itself, which may already hold
-            # the sum of earlier micro-batches
-            sp = g.params[self.index].sharded_param
-            accumulate = sp is not None and sp.grad is not None
+        accumulate = self.would_accumulate()
         g._sink_written[self.index] = True
         if zero and not accumulate:
             self.view.zero_()
@@ -391,6 +424,12 @@ class ParamGroup:
         self.post_reduce_hook: Callable[[torch.Tensor], None] | None = None
         # True: this group never shares its gather / reduce buffers with the rotating ones
         self.dedicated_buffers = False
+        # fused gradient reduction (peer-memory backend, fp32 reduce): weight-gradient GEMMs push their rows from the epilogue
+        # into the owners' reduce-scatter slots, the owners sum their slots locally; every parameter of the group must get
+        # exactly one gradient per backward pass
+        self.fused_reduce = False
+        self._push_ptrs: Any = None
+        self._pushed = False
         # hierarchical partitioning: a secondary shard of the gathered weights kept inside a smaller (intra-node) group
         self.secondary_group: dist.ProcessGroup | None = None
         self._secondary_shard: torch.Tensor | None = None
@@ -538,6 +577,12 @@ class ParamGroup:
                        and sp.ext_cls is None else None)
             if sp.unsharded_param is not None:
                 sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
+        self._push_ptrs = None
+        if (grad_flat is not None and not self._alias_grad and hasattr(backend, "reduce_pushed")
+                and self.reduce_scatter_dtype == torch.float32 and self.layout.shard_numel % 4 == 0
+                and all(sp.numel % 4 == 0 and sp.sink is not None for sp in self.params if sp.requires_grad)
+                and all(sp.requires_grad for sp in self.params)):
+            self._push_ptrs = backend.peer_pointers(grad_flat)  # type: ignore[attr-defined]
         self._register_state_dict_hooks()
         self._lazy_inited = True
 
@@ -761,6 +806,15 @@ class ParamGroup:
             target.unshard(target.unshard_async_op)
             target._training_state = old
 
+    def _push_mode(self) -> bool:
+        """Gradients of this backward pass go to their owners from the producing kernels.  Decided by the first gradient
+        of the pass: not while unreduced gradients of earlier micro-batches sit in the local flat buffer."""
+        if self._pushed:
+            return True
+        if not (self.fused_reduce and self.reduce_grads and self._push_ptrs is not None) or self.post_reduce_hook is not None:
+            return False
+        return not (self._holds_grad_buffer and any(self._sink_written))
+
     def _acquire_grad_buffer(self) -> None:
         if self._holds_grad_buffer or self._alias_grad:
             self._holds_grad_buffer = True
@@ -793,6 +847,14 @@ class ParamGroup:
             if not with_grad:
                 if self.reshard_after_backward:
                     self.reshard()
+                return
+            if self._pushed:
+                self._finish_pushes()
+                with record_function(self._with_fqn("YaFSDP::post_backward_reshard")):
+                    if self.reshard_after_backward:
+                        self.reshard()
+                with record_function(self._with_fqn("YaFSDP::post_backward_reduce")):
+                    self._reduce([sp for sp in self.params if sp.requires_grad], st)
                 return
             self._acquire_grad_buffer()
             fresh = self._alias_grad and not self._has_sharded_grads()
@@ -835,6 +897,22 @@ class ParamGroup:
         with record_function(self._with_fqn("YaFSDP::post_backward_reduce")):
             self._reduce(with_grad, st)
 
+    def _finish_pushes(self) -> None:
+        """End of a backward pass in push mode: gradients that autograd produced (``.grad``) are pushed now, parameters
+        that got no gradient push zeros, so every position of every owner's slot for this rank has been written."""
+        with torch.no_grad():
+            for sp in self.params:
+                if not sp.requires_grad:
+                    continue
+                up = sp.unsharded_param
+                g = up.grad if up is not None else None
+                assert sp.sink is not None
+                if g is not None:
+                    up.grad = None  # type: ignore[union-attr]
+                    sp.sink.push_from(g.to(torch.float32).contiguous())
+                elif not self._sink_written[sp.index]:
+                    sp.sink.push_from(None)
+
     def _has_sharded_grads(self) -> bool:
         return any(sp.sharded_param is not None and sp.sharded_param.grad is not None for sp in self.params)
 
@@ -871,7 +949,29 @@ class ParamGroup:
             if pre is not None and pre != 1.0:
                 self._grad_flat.div_(pre)
             dst = self.sharded_grad_flat
-            if (all_fresh or all_have) and self.post_reduce_hook is None:
+            if self._pushed:
+                # every rank's contribution already sits in this rank's slots: wait for all of them, sum locally
+                self._pushed = False
+                whole = all_fresh or all_have
+                target = self._norm_sq if (self._norm_sq is not None and all_fresh and dst.dtype == torch.float32) else None
+                if target is not None:
+                    target.zero_()
+                out = dst if whole else torch.empty_like(dst)
+                fused = self.comm_ctx.backend.reduce_pushed(  # type: ignore[attr-defined]
+                    out, self._grad_flat, scale=scale, accumulate=whole and not all_fresh, sumsq=target if whole else None,
+                    valid_numel=self.layout.total_numel)
+                self._norm_fused_ok = bool(fused)
+                if not whole:
+                    for sp in with_grad:
+                        pl = sp.placement
+                        assert pl is not None
+                        src = out[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                        tgt = dst[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                        if had[sp.index]:
+                            tgt.add_(src)
+                        else:
+                            tgt.copy_(src)
+            elif (all_fresh or all_have) and self.post_reduce_hook is None:
                 # the reduction kernel can also sum the squares of the final shard (gradient-norm fusion) when this is the
                 # only contribution of the step to the sharded gradient
                 target = self._norm_sq if (self._norm_sq is not None and all_fresh and dst.dtype == torch.float32) else None
@@ -1084,6 +1184,22 @@ class GroupSet:
     @property
     def _unshard_pending(self) -> bool:
         return any(g._unshard_pending for g in self.groups)
+
+    def _finish_pushes(self) -> None:
+        """End of a backward pass in push mode: gradients that autograd produced (``.grad``) are pushed now, parameters
+        that got no gradient push zeros, so every position of every owner's slot for this rank has been written."""
+        with torch.no_grad():
+            for sp in self.params:
+                if not sp.requires_grad:
+                    continue
+                up = sp.unsharded_param
+                g = up.grad if up is not None else None
+                assert sp.sink is not None
+                if g is not None:
+                    up.grad = None  # type: ignore[union-attr]
+                    sp.sink.push_from(g.to(torch.float32).contiguous())
+                elif not self._sink_written[sp.index]:
+                    sp.sink.push_from(None)
 
     def _has_sharded_grads(self) -> bool:
         return any(g._has_sharded_grads() for g in self.groups)

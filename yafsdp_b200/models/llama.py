@@ -12,6 +12,8 @@ layer, ``[norm, lm_head]`` as one group, then a parameter-less root.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Any
 
@@ -238,8 +240,9 @@ def _run_head(norm: RMSNorm, lm_head: LMHead, h: torch.Tensor, labels: torch.Ten
 
 
 def shard_llama(model: LlamaForCausalLM, *, mesh: Any = None, mp_policy: MixedPrecisionPolicy | None = None,
-                reshard_after_forward: bool | None = True, comm_backend: str | None = None,
-                num_grad_buffers: int | None = 2, checkpoint_layers: int = 0) -> LlamaForCausalLM:
+                reshard_after_forward: bool | None = True, comm_backend: Any = None,
+                num_grad_buffers: int | None = 2, checkpoint_layers: int = 0, fused_reduce: bool | None = None,
+                **backend_options: Any) -> LlamaForCausalLM:
     """Wrap a Llama model: embedding, each decoder layer and ``[norm, lm_head]`` become groups, the model itself the
     parameter-less root.  ``checkpoint_layers`` wraps the first N layers' forward in activation checkpointing."""
     mp_policy = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
@@ -256,6 +259,14 @@ def shard_llama(model: LlamaForCausalLM, *, mesh: Any = None, mp_policy: MixedPr
         raise NotImplementedError("shard_llama: tied embeddings are not supported (wrap embed_tokens, norm and lm_head as one group yourself)")
     fully_shard([model.model.norm, model.lm_head], **kw)
     fully_shard(model, **kw)
+    if fused_reduce is None:
+        fused_reduce = os.environ.get("YAFSDP_FUSED_REDUCE", "0") == "1"
+    if fused_reduce:
+        # decoder layers and the head use every weight once per backward pass: their weight-gradient GEMMs push straight to
+        # the owners (the embedding's gradient comes from a scatter-add kernel and stays on the unfused path)
+        for layer in model.model.layers:
+            layer.set_fused_gradient_reduce(True)  # type: ignore[attr-defined]
+        model.lm_head.set_fused_gradient_reduce(True)  # type: ignore[attr-defined]
     if comm_backend is not None or num_grad_buffers is not None:
-        model.set_comm_backend(comm_backend or "torch", num_grad_buffers=num_grad_buffers)  # type: ignore[attr-defined]
+        model.set_comm_backend(comm_backend or "torch", num_grad_buffers=num_grad_buffers, **backend_options)  # type: ignore[attr-defined]
     return model

@@ -78,6 +78,20 @@ class _WeightGrad:
 
     def run(self, dy: torch.Tensor, x: torch.Tensor) -> list[torch.Tensor | None]:
         """dW = dy^T x for the fused weight; returns per-parameter gradients (None when sunk)."""
+        if self.use_sinks and all(s.pushes() for s in self.sinks):
+            # fused GEMM -> reduce-scatter: parameters that follow each other in the flat gradient are one GEMM
+            i, r0 = 0, 0
+            while i < len(self.sinks):
+                ptrs, off, shard, rank, world = self.sinks[i].begin_push()
+                rows, nxt, j = self.params[i].shape[0], off + self.params[i].numel(), i + 1
+                while j < len(self.sinks) and self.sinks[j].group is self.sinks[i].group:
+                    _, off_j, *_ = self.sinks[j].begin_push()
+                    assert off_j == nxt, "fused weights must be adjacent in the flat layout"
+                    rows, nxt, j = rows + self.params[j].shape[0], nxt + self.params[j].numel(), j + 1
+                kernels.gemm_scatter(dy[:, r0 : r0 + rows], x, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off,
+                                     shard_numel=shard, rank=rank, world=world)
+                i, r0 = j, r0 + rows
+            return [None] * len(self.params)
         if self.use_sinks:
             views, accs = zip(*[s.begin() for s in self.sinks])
             fused = fuse_adjacent(list(views)) if len(views) > 1 else views[0]
@@ -102,10 +116,18 @@ class _WeightGrad:
 def _norm_weight_grad(w: torch.Tensor, fn: Any) -> torch.Tensor | None:
     """Run ``fn(dw_fp32)`` (a kernel that atomically accumulates into dw); returns the gradient unless sunk."""
     s = _sink(w)
+    if s is not None and s.pushes():
+        dw = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        fn(dw)
+        s.push_from(dw)
+        return None
     if s is not None:
+        zeroed_now = not s.would_accumulate()
         view, _ = s.begin(zero=True)
         fn(view)
-        tgt = s.norm_target(s.group._sink_written_twice(s.index))
+        # the value is final (and its squares may be summed here) only if this call started from zeros: an earlier write
+        # of this backward pass or an earlier micro-batch's gradient makes it a partial sum
+        tgt = s.norm_target(not zeroed_now)
         if tgt is not None:
             kernels.sumsq_(view.reshape(-1), tgt)
         return None

@@ -44,7 +44,9 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 def status(clear: bool = True) -> tuple[int, int]:
-    """(code, site) of the first error any kernel recorded since the last clearing read.  Synchronises."""
+    """(code, site) of the first error any kernel recorded since the last clearing read.  The status word sits in host
+    memory: this is a plain read that neither synchronises nor touches the GPU; synchronise first to cover kernels that
+    are still running."""
     code = ctypes.c_int(0)
     site = ctypes.c_int(0)
     rc = _native.lib().yf_status_read(ctypes.byref(code), ctypes.byref(site), int(clear))
@@ -56,7 +58,15 @@ def status(clear: bool = True) -> tuple[int, int]:
 def check_status() -> None:
     code, site = status()
     if code != 0:
-        raise RuntimeError(f"a native kernel reported error {code} at site {site} (bounded wait ran out)")
+        raise RuntimeError(f"a native kernel reported error {code} at site {site} (a bounded wait ran out: a peer rank is late or "
+                           "gone); the results of the kernels that ran since are undefined")
+
+
+def poll_status() -> None:
+    """:func:`check_status` when the native library is loaded in this process, nothing otherwise (CPU runs).  Cheap enough
+    for once per step: the framework calls it at every root pre-forward and in the fused optimizer step."""
+    if _native.loaded():
+        check_status()
 
 
 # --------------------------------------------------------------------------------------- GEMM
@@ -133,6 +143,15 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool, b_mn_maj
                                             int(b_mn_major), float(alpha), peer_grad, c_flat_off, shard_numel, rank, world,
                                             int(sm_limit), _stream())
     _check(rc, "yf_gemm_bf16_scatter")
+
+
+def push_flat(src: torch.Tensor | None, numel: int, flat_off: int, peer_grad: Any, shard_numel: int, rank: int, world: int) -> None:
+    """Push ``numel`` fp32 values (``src``, or zeros when ``None``) that start at position ``flat_off`` of the flat layer
+    gradient into the owners' reduce-scatter slots for this rank."""
+    if src is not None:
+        assert src.dtype == torch.float32 and src.is_contiguous() and src.numel() == numel
+    rc = _native.lib().yf_push_flat(_ptr(src), numel, flat_off, peer_grad, shard_numel, rank, world, _stream())
+    _check(rc, "yf_push_flat")
 
 
 # --------------------------------------------------------------------------------------- norms etc.

@@ -99,22 +99,29 @@ class ShardedAdamW:
 
         dev = self._norm_sq.device
         self._norm_sq.zero_()
-        fused = []
+        # groups may be sharded over different process groups: sum each group's shards over its own ranks
+        by_pg: dict[Any, list[int]] = {}
         for i in active:
-            grp = self.groups[i]
-            if grp._norm_sq is not None and grp._norm_fused_ok:
-                fused.append(i)  # the kernels that wrote the gradients already summed their squares
-                continue
-            g = grp.sharded_grad_flat
-            if dev.type == "cuda":
-                kernels.sumsq_(g, self._norm_sq)
-            else:
-                self._norm_sq += g.float().pow(2).sum()
-        if fused:
-            self._norm_sq += self._group_norm_sq[fused].sum() if len(fused) < len(self.groups) else self._group_norm_sq.sum()
-        pg = self.groups[0].process_group
-        if pg is not None and pg.size() > 1:
-            dist.all_reduce(self._norm_sq, group=pg)
+            by_pg.setdefault(self.groups[i].process_group, []).append(i)
+        for n_pg, (pg, members) in enumerate(by_pg.items()):
+            part = self._norm_sq if len(by_pg) == 1 else torch.zeros_like(self._norm_sq)
+            fused = []
+            for i in members:
+                grp = self.groups[i]
+                if grp._norm_sq is not None and grp._norm_fused_ok:
+                    fused.append(i)  # the kernels that wrote the gradients already summed their squares
+                    continue
+                g = grp.sharded_grad_flat
+                if dev.type == "cuda":
+                    kernels.sumsq_(g, part)
+                else:
+                    part += g.float().pow(2).sum()
+            if fused:
+                part += self._group_norm_sq[fused].sum() if len(fused) < len(self.groups) else self._group_norm_sq.sum()
+            if pg is not None and pg.size() > 1:
+                dist.all_reduce(part, group=pg)
+            if part is not self._norm_sq:
+                self._norm_sq += part
         if dev.type == "cuda":
             kernels.clip_coef_(self._norm_sq, self.max_grad_norm, self._coef, self.last_grad_norm)
         else:
@@ -128,6 +135,10 @@ class ShardedAdamW:
         active = self._active()
         if not active:
             return
+        if self._norm_sq.is_cuda:
+            from .ops import kernels
+
+            kernels.poll_status()
         self.step_count += 1
         coef = self._compute_clip_coef(active)
         b1, b2 = self.betas
@@ -261,21 +272,29 @@ def clip_grad_norm_(parameters: Iterable[torch.Tensor] | nn.Module, max_norm: fl
     if not grads:
         return torch.zeros(())
     dev = grads[0].device
-    total = torch.zeros((), device=dev, dtype=torch.float32)
-    sharded_group = None
+    inf = norm_type == math.inf
+
+    def fold(acc: torch.Tensor, local: torch.Tensor) -> torch.Tensor:
+        if inf:
+            return torch.maximum(acc, local.abs().max().float()) if local.numel() else acc
+        return acc + local.float().abs().pow(norm_type).sum()
+
+    # sharded gradients: every rank holds a piece, summed (or maximised) over the ranks of their shard group; plain
+    # gradients (replicated or ignored parameters) are whole on every rank and enter once
+    plain = torch.zeros((), device=dev, dtype=torch.float32)
+    sharded: dict[Any, torch.Tensor] = {}
     for g in grads:
         if isinstance(g, RaggedShardDTensor):
-            local = g._local_tensor
-            sharded_group = g._spec.group() or sharded_group
+            pg = g._spec.group()
+            sharded[pg] = fold(sharded.get(pg, torch.zeros((), device=dev, dtype=torch.float32)), g._local_tensor)
         else:
-            local = g
-        if norm_type == math.inf:
-            total = torch.maximum(total, local.abs().max().float() if local.numel() else total)
-        else:
-            total = total + local.float().abs().pow(norm_type).sum()
-    if sharded_group is not None and sharded_group.size() > 1:
-        dist.all_reduce(total, op=dist.ReduceOp.MAX if norm_type == math.inf else dist.ReduceOp.SUM, group=sharded_group)
-    if norm_type != math.inf:
+            plain = fold(plain, g)
+    total = plain
+    for pg, part in sharded.items():
+        if pg is not None and pg.size() > 1:
+            dist.all_reduce(part, op=dist.ReduceOp.MAX if inf else dist.ReduceOp.SUM, group=pg)
+        total = torch.maximum(total, part) if inf else total + part
+    if not inf:
         total = total.pow(1.0 / norm_type)
     coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
     for g in grads:

@@ -63,7 +63,8 @@ class FSDPState:
         self._states_to_forward_prefetch: list[FSDPState] = []
         self._states_to_backward_prefetch: list[FSDPState] = []
         self._module_fqn: str | None = None
-        self._backend_name: str | None = None
+        self._backend_name: Any = None
+        self._backend_options: dict[str, Any] = {}
         self._num_grad_buffers: int | None = None
         self._outer: FSDPState | None = None  # state of the enclosing fully_shard module, if any
 
@@ -115,6 +116,10 @@ class FSDPState:
             return args, kwargs
         logger.debug("root pre-forward")
         self._state_ctx.iter_forward_root = self
+        if self._device.type == "cuda":
+            from .ops import kernels
+
+            kernels.poll_status()  # a bounded device-side wait that ran out during the previous step surfaces here
         with record_function("YaFSDP::root_pre_forward"):
             st = self._comm_ctx.streams
             assert st is not None
@@ -204,7 +209,7 @@ class FSDPState:
         if isinstance(comm_backend, CommBackend):
             backend = comm_backend
         else:
-            backend = make_backend(comm_backend, self._device, pg)
+            backend = make_backend(comm_backend, self._device, pg, **self._backend_options)
         self._comm_ctx.lazy_init(self._device, backend)
         for s in self._state_ctx.all_states:
             s._state_ctx = self._state_ctx

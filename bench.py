@@ -26,7 +26,6 @@ import torch
 import torch.distributed as dist
 
 REPO = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, REPO)
 
 PUBLISHED_TOKENS_PER_S_PER_GPU = 2528.0  # reference README: Llama-2-7B, seq 2048, 64xA100-80G, 0.81 s / iteration
 
@@ -146,6 +145,16 @@ def run(args, make_step) -> dict:
     step_e2e(host_batches[0])  # one untimed pass through the end-to-end path
     ms_e2e = timed_steps(step_e2e, host_batches, args.steps, device, finish)
     clocks = sampler.stop() if rank == 0 else {}
+    # exposed communication, measured: the same steps once more with the collectives moving nothing between the GPUs
+    # (compute-only step at this world size; the values it computes are meaningless, it runs last)
+    ms_dry = None
+    dry = extra.pop("_dry_run", None)
+    if dry is not None and world > 1:
+        dry(True)
+        for i in range(2):
+            step_dev(dev_batches[i % n_batches])
+        ms_dry = timed_steps(step_dev, dev_batches, args.steps, device, finish)
+        dry(False)
     # host time to issue one step into an empty queue (no device wait inside): when it approaches ms_per_step the step is
     # bound by the launching CPU thread, not by the GPU
     torch.cuda.synchronize()
@@ -178,10 +187,11 @@ def run(args, make_step) -> dict:
             "seq_len": seq,
             "parallelism": f"dp{world} fully sharded (ZeRO-3)",
             "optimizer": "AdamW fp32 master/grad/moments, global-norm clip 1.0",
-            "activation_checkpointing": 0,
+            "activation_checkpointing": args.checkpoint_layers,
+            "params": extra.pop("params"),
             "l2": "no explicit flush: every step streams far more than the 126 MB L2 (weights, gradients, optimizer state)",
             "vs_baseline_is": "tokens/s/GPU over the reference's published 2528 tokens/s/GPU (64xA100-80G)",
-            **extra,
+            "impl_detail": extra,
         },
         "clocks": clocks,
         "e2e": {
@@ -196,6 +206,10 @@ def run(args, make_step) -> dict:
         "peak_mem_gb": round(peak_gb, 2),
         "host_issue_ms_per_step": round(host_issue_ms, 2),
     }
+    if ms_dry is not None:
+        result["compute_only_ms_per_step"] = round(ms_dry / args.steps, 3)
+        result["exposed_comm_ms"] = round((ms - ms_dry) / args.steps, 3)
+        result["exposed_comm_fraction"] = round((ms - ms_dry) / ms, 4)
     if rank == 0:
         print(json.dumps(result), flush=True)
     dist.destroy_process_group()
@@ -210,7 +224,7 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
     from yafsdp_b200.train import TrainStep, build_llama
 
     cfg = CONFIGS[args.model]
-    model = build_llama(cfg, device, comm_backend=args.comm_backend)
+    model = build_llama(cfg, device, comm_backend=args.comm_backend, checkpoint_layers=args.checkpoint_layers)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, device)
 
@@ -221,8 +235,18 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
         return step(ids_host).item()
 
     backend = args.comm_backend if args.comm_backend != "auto" else ("symm" if world > 1 else "none (single rank: buffers aliased)")
-    return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, {
-        "comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join}
+
+    def dry_run(on: bool) -> None:
+        be = model._get_fsdp_state()._comm_ctx.backend
+        if hasattr(be, "dry_run"):
+            torch.cuda.synchronize()
+            dist.barrier()
+            be.dry_run = on
+
+    detail = {"comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join}
+    if backend == "symm":
+        detail["_dry_run"] = dry_run
+    return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, detail
 
 
 # ----------------------------------------------------------------------------------------- reference
@@ -260,6 +284,12 @@ def make_step_reference(args, rank: int, world: int, device: torch.device):
     kw = dict(mesh=mesh, mp_policy=mp)
     if world == 1:
         kw["reshard_after_forward"] = False
+    if args.checkpoint_layers:
+        # the reference's recipe: non-reentrant activation checkpointing on the first N decoder layers, applied before sharding
+        from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import CheckpointImpl, checkpoint_wrapper
+
+        for i in range(min(args.checkpoint_layers, len(model.model.layers))):
+            model.model.layers[i] = checkpoint_wrapper(model.model.layers[i], checkpoint_impl=CheckpointImpl.NO_REENTRANT)
     ya_fsdp.fully_shard(model.model.embed_tokens, **kw)
     for layer in model.model.layers:
         ya_fsdp.fully_shard(layer, **kw)
@@ -299,6 +329,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1, help="sequences per GPU")
     ap.add_argument("--comm-backend", default="auto", choices=["auto", "torch", "symm"])
     ap.add_argument("--ref-attn", default="sdpa", choices=["sdpa", "flash_attention_2", "eager"])
+    ap.add_argument("--checkpoint-layers", type=int, default=0, help="activation checkpointing on the first N decoder layers")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

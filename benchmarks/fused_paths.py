@@ -6,10 +6,11 @@ Run under torchrun on N GPUs of one box::
 
 Reports (device-timed with CUDA events, max over ranks, inputs far larger than L2):
 
-* all-gather -> GEMM: the layer's bf16 all-gather (pull) followed by the QKV GEMM, unfused vs the single fused
-  kernel; roofline = max(GEMM FLOPs / measured bf16 peak, bytes that must cross NVLink / 770 GB/s);
-* GEMM -> reduce-scatter: the layer's weight-gradient GEMMs (fp32) + pull reduce-scatter, unfused vs epilogue
-  push + local slot reduction; same roofline rule.
+* all-gather -> GEMM: the layer's bf16 all-gather (copy engines or pull kernel) followed by the QKV GEMM, unfused vs the
+  single fused kernel; roofline = max(GEMM FLOPs / measured bf16 peak, bytes that must cross NVLink / 770 GB/s);
+* GEMM -> reduce-scatter: the layer's weight-gradient GEMMs (fp32) + reduce-scatter, unfused vs epilogue push + local
+  slot reduction, one layer at a time and pipelined as in a backward pass (two rotating buffers, the reduction on a side
+  stream under the next layer's GEMMs); same roofline rule.
 """
 
 from __future__ import annotations
@@ -21,9 +22,12 @@ import sys
 import torch
 import torch.distributed as dist
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+try:
+    import yafsdp_b200  # noqa: F401  (installed: pip install -e . --no-build-isolation)
+except ImportError:  # run from a checkout that was not installed
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from yafsdp_b200.comm.symm import SymmBackend, _ptr_array  # noqa: E402
+from yafsdp_b200.comm.symm import SymmBackend  # noqa: E402
 from yafsdp_b200.ops import kernels  # noqa: E402
 
 NVLINK_GBS = 770.0
@@ -71,7 +75,7 @@ def main() -> None:
     inp = be.alloc(shard, torch.bfloat16, dev, "gather_input")
     inp.copy_(torch.randn(shard, device=dev).bfloat16() * 0.02)
     layer = torch.empty(total, device=dev, dtype=torch.bfloat16)
-    flags = torch.zeros(world * 1024 + 64, device=dev, dtype=torch.int32)
+    counters = torch.zeros(3 * d // 128, device=dev, dtype=torch.int64)
     out = torch.empty(t, 3 * d, device=dev, dtype=torch.bfloat16)
     torch.cuda.synchronize()
     be.step_barrier()
@@ -85,17 +89,27 @@ def main() -> None:
     def fused_ag_gemm():
         epoch[0] += 1
         kernels.gemm_gathered(x, 3 * d, d, peer_in=be._peers(inp), layer_buf=layer, shard_bytes=shard * 2, b_byte_off=qkv_off * 2,
-                              rank=rank, world=world, flags=flags, epoch=epoch[0], chunk_bytes=1 << 20, n_comm=int(os.environ.get("YF_NCOMM", "32")),
-                              out=out)
+                              rank=rank, world=world, counters=counters, epoch=epoch[0], out=out)
 
-    t_ag = timed(lambda: be.all_gather(layer, inp, None), dev)
     t_gemm = timed(lambda: kernels.gemm(x, wqkv, out=out), dev)
-    t_unf = timed(unfused_ag_gemm, dev)
+    t_ag, t_unf = {}, {}
+    for tr in ("ce", "sm"):
+        be.set_transports(ag=tr)
+        t_ag[tr] = timed(lambda: be.all_gather(layer, inp, None), dev)
+        t_unf[tr] = timed(unfused_ag_gemm, dev)
     t_fus = timed(fused_ag_gemm, dev)
+    # the fused kernel must leave the same bytes behind as the plain all-gather
+    be.set_transports(ag="ce")
+    be.all_gather(layer, inp, None)
+    want = layer.clone()
+    layer.zero_()
+    fused_ag_gemm()
+    torch.cuda.synchronize()
+    same = bool(torch.equal(layer, want))
     flops = 2.0 * t * 3 * d * d
     roof_ag = max(flops / (peak * 1e9), (world - 1) * shard * 2 / (NVLINK_GBS * 1e6))  # ms
-    # ---- gradient side: dW of the four fused weights, fp32
-    gbuf = be.alloc(total, torch.float32, dev, "reduce_input")
+    # ---- gradient side: dW of the four fused weights, fp32, two reduce buffers in rotation as in a backward pass
+    gbufs = [be.alloc(total, torch.float32, dev, "reduce_input") for _ in range(2)]
     dst = torch.zeros(shard, device=dev, dtype=torch.float32)
     acts = {
         "qkv": (torch.randn(t, 3 * d, device=dev).bfloat16(), x, d),
@@ -103,33 +117,28 @@ def main() -> None:
         "gateup": (torch.randn(t, 2 * f, device=dev).bfloat16(), x, d + 4 * d * d + d),
         "down": (torch.randn(t, d, device=dev).bfloat16(), torch.randn(t, f, device=dev).bfloat16(), d + 4 * d * d + d + 2 * f * d),
     }
-    local_slots = _ptr_array([gbuf.data_ptr() + (r - rank) * shard * 4 for r in range(world)])
 
-    def unfused_dw_rs():
-        for dy, xx, off in acts.values():
-            view = gbuf[off : off + dy.shape[1] * xx.shape[1]].view(dy.shape[1], xx.shape[1])
-            kernels.gemm(dy, xx, a_mn_major=True, b_mn_major=True, out=view)
-        be.reduce_scatter(dst, gbuf, None, scale=1.0 / world, accumulate=False)
-
-    def fused_dw_rs():
-        for dy, xx, off in acts.values():
-            kernels.gemm_scatter(dy, xx, a_mn_major=True, b_mn_major=True, peer_grad=be._peers(gbuf), c_flat_off=off, shard_numel=shard,
-                                 rank=rank, world=world)
-        be.barrier(1)
-        rc = kernels._native.lib().yf_reduce_scatter_pull(local_slots, dst.data_ptr(), shard, rank, world, 1.0 / world, 0, 0, 0,
-                                                          torch.cuda.current_stream().cuda_stream)
-        assert rc == 0
-        be.barrier(2)
-
-    def dw_only():
+    def dw_local(gbuf):
         for dy, xx, off in acts.values():
             view = gbuf[off : off + dy.shape[1] * xx.shape[1]].view(dy.shape[1], xx.shape[1])
             kernels.gemm(dy, xx, a_mn_major=True, b_mn_major=True, out=view)
 
-    def scatter_only():
+    def dw_pushed(gbuf):
+        ptrs = be._peers(gbuf)
         for dy, xx, off in acts.values():
-            kernels.gemm_scatter(dy, xx, a_mn_major=True, b_mn_major=True, peer_grad=be._peers(gbuf), c_flat_off=off, shard_numel=shard,
+            kernels.gemm_scatter(dy, xx, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off, shard_numel=shard,
                                  rank=rank, world=world)
+
+    def serial(fused: bool):
+        def run():
+            be.before_write(gbufs[0])
+            if fused:
+                dw_pushed(gbufs[0])
+                be.reduce_pushed(dst, gbufs[0], scale=1.0 / world, accumulate=False)
+            else:
+                dw_local(gbufs[0])
+                be.reduce_scatter(dst, gbufs[0], None, scale=1.0 / world, accumulate=False)
+        return run
 
     # steady state of a backward pass: the reduction of layer l runs on a side stream under the GEMMs of layer l+1
     side = torch.cuda.Stream()
@@ -137,47 +146,67 @@ def main() -> None:
 
     def pipelined(fused: bool):
         def run():
-            for _ in range(n_layers):
-                scatter_only() if fused else dw_only()
+            cur = torch.cuda.current_stream()
+            released = [None, None]
+            for l in range(n_layers):
+                g = gbufs[l % 2]
+                if released[l % 2] is not None:
+                    cur.wait_event(released[l % 2])
+                be.before_write(g)
+                dw_pushed(g) if fused else dw_local(g)
                 ev = torch.cuda.Event()
                 ev.record()
                 with torch.cuda.stream(side):
                     side.wait_event(ev)
                     if fused:
-                        be.barrier(1)
-                        kernels._native.lib().yf_reduce_scatter_pull(local_slots, dst.data_ptr(), shard, rank, world, 1.0 / world, 0, 0, 0,
-                                                                     side.cuda_stream)
-                        be.barrier(2)
+                        be.reduce_pushed(dst, g, scale=1.0 / world, accumulate=False)
                     else:
-                        be.reduce_scatter(dst, gbuf, None, scale=1.0 / world, accumulate=False)
+                        be.reduce_scatter(dst, g, None, scale=1.0 / world, accumulate=False)
                     done = torch.cuda.Event()
                     done.record()
-                torch.cuda.current_stream().wait_event(done) if False else None
-            torch.cuda.current_stream().wait_stream(side)
+                released[l % 2] = done
+            cur.wait_stream(side)
         return run
 
-    t_dw = timed(dw_only, dev)
-    t_scatter = timed(scatter_only, dev)
-    t_pipe_unf = timed(pipelined(False), dev) / n_layers
+    be.set_transports(rs="sm")
+    t_dw = timed(lambda: dw_local(gbufs[0]), dev)
+    t_rs = {}
+    t_unf2, t_pipe_unf = {}, {}
+    for tr in ("sm", "ce"):
+        be.set_transports(rs=tr)
+        t_rs[tr] = timed(lambda: (be.before_write(gbufs[0]), be.reduce_scatter(dst, gbufs[0], None, scale=1.0 / world, accumulate=False)), dev)
+        t_unf2[tr] = timed(serial(False), dev)
+        t_pipe_unf[tr] = timed(pipelined(False), dev) / n_layers
+    t_fus2 = timed(serial(True), dev)
     t_pipe_fus = timed(pipelined(True), dev) / n_layers
-    t_rs = timed(lambda: be.reduce_scatter(dst, gbuf, None, scale=1.0 / world, accumulate=False), dev)
-    t_unf2 = timed(unfused_dw_rs, dev)
-    t_fus2 = timed(fused_dw_rs, dev)
+    # pushed GEMMs alone (nobody sums the slots): the epilogue's store rate over NVLink
+    torch.cuda.synchronize()
+    dist.barrier()
+    be.before_write(gbufs[0])
+    be.before_write(gbufs[1])
+    t_scatter = timed(lambda: dw_pushed(gbufs[0]), dev)
     flops2 = 2.0 * t * (4 * d * d + 3 * f * d)
     roof_rs = max(flops2 / (peak * 1e9), (world - 1) * shard * 4 / (NVLINK_GBS * 1e6))
     code, site = kernels.status()
     if rank == 0:
+        best_unf = min(t_unf.values())
+        best_unf2 = min(t_unf2.values())
         print(json.dumps({
             "n_gpus": world, "layer_params": sum(numels), "bf16_peak_tflops_measured": peak, "nvlink_gbs": NVLINK_GBS, "status": [code, site],
-            "ag_gemm": {"all_gather_ms": round(t_ag, 4), "gemm_ms": round(t_gemm, 4), "unfused_ms": round(t_unf, 4), "fused_ms": round(t_fus, 4),
+            "ag_gemm": {"all_gather_ms": {k: round(v, 4) for k, v in t_ag.items()}, "gemm_ms": round(t_gemm, 4),
+                        "unfused_ms": {k: round(v, 4) for k, v in t_unf.items()}, "fused_ms": round(t_fus, 4),
+                        "fused_layer_buffer_equals_all_gather": same,
                         "roofline_ms": round(roof_ag, 4), "fused_fraction_of_roofline": round(roof_ag / t_fus, 3),
-                        "unfused_fraction_of_roofline": round(roof_ag / t_unf, 3)},
-            "gemm_rs": {"dw_gemms_ms": round(t_dw, 4), "scatter_gemms_ms": round(t_scatter, 4),
-                        "scatter_gemms_fraction_of_roofline": round(roof_rs / t_scatter, 3),
-                        "pipelined_per_layer_unfused_ms": round(t_pipe_unf, 4), "pipelined_per_layer_fused_ms": round(t_pipe_fus, 4),
-                        "pipelined_fused_fraction_of_roofline": round(roof_rs / t_pipe_fus, 3), "reduce_scatter_ms": round(t_rs, 4), "unfused_ms": round(t_unf2, 4), "fused_ms": round(t_fus2, 4),
+                        "best_unfused_fraction_of_roofline": round(roof_ag / best_unf, 3)},
+            "gemm_rs": {"dw_gemms_ms": round(t_dw, 4), "pushed_gemms_ms": round(t_scatter, 4),
+                        "pushed_gemms_fraction_of_roofline": round(roof_rs / t_scatter, 3),
+                        "reduce_scatter_ms": {k: round(v, 4) for k, v in t_rs.items()},
+                        "unfused_ms": {k: round(v, 4) for k, v in t_unf2.items()}, "fused_ms": round(t_fus2, 4),
+                        "pipelined_per_layer_unfused_ms": {k: round(v, 4) for k, v in t_pipe_unf.items()},
+                        "pipelined_per_layer_fused_ms": round(t_pipe_fus, 4),
                         "roofline_ms": round(roof_rs, 4), "fused_fraction_of_roofline": round(roof_rs / t_fus2, 3),
-                        "unfused_fraction_of_roofline": round(roof_rs / t_unf2, 3)},
+                        "pipelined_fused_fraction_of_roofline": round(roof_rs / t_pipe_fus, 3),
+                        "best_unfused_fraction_of_roofline": round(roof_rs / best_unf2, 3)},
         }))
     dist.destroy_process_group()
 

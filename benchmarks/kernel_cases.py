@@ -19,7 +19,10 @@ import sys
 
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+try:
+    import yafsdp_b200  # noqa: F401  (installed: pip install -e . --no-build-isolation)
+except ImportError:  # run from a checkout that was not installed
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from yafsdp_b200.ops import kernels  # noqa: E402
 

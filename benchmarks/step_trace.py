@@ -31,7 +31,10 @@ import torch
 import torch.distributed as dist
 from torch.profiler import ProfilerActivity, profile
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+try:
+    import yafsdp_b200  # noqa: F401  (installed: pip install -e . --no-build-isolation)
+except ImportError:  # run from a checkout that was not installed
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from yafsdp_b200.models.llama import CONFIGS  # noqa: E402
 from yafsdp_b200.optim import ShardedAdamW  # noqa: E402

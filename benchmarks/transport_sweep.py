@@ -7,7 +7,8 @@ The model is built once (multicast arena when the box has NVSwitch multicast), t
 measurements with ``SymmBackend.set_transports``: a configuration costs a few steps, not a start-up.  A configuration is
 ``<all-gather>[:CTAs]/<reduce-scatter>[:CTAs][+1s]`` with transports ``ce`` (copy engines), ``sm`` (pull kernels),
 ``mc`` (NVSwitch multicast); ``+1s`` puts both collectives on one communication stream, ``+fr`` fuses the gradient
-reduce-scatter into the weight-gradient GEMMs (rows pushed to their owners from the epilogue).  Rank 0 prints one JSON line per
+reduce-scatter into the weight-gradient GEMMs (rows pushed to their owners from the epilogue).  The configuration ``dry``
+times the step with collectives that move nothing (compute-only step at this world size); put it last.  Rank 0 prints one JSON line per
 configuration: CUDA-event time of ``--steps`` steps, max over ranks.
 """
 
@@ -21,7 +22,10 @@ import sys
 import torch
 import torch.distributed as dist
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+try:
+    import yafsdp_b200  # noqa: F401  (installed: pip install -e . --no-build-isolation)
+except ImportError:  # run from a checkout that was not installed
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from yafsdp_b200.models.llama import CONFIGS  # noqa: E402
 from yafsdp_b200.ops import kernels  # noqa: E402
@@ -54,9 +58,14 @@ def main() -> None:
     be = cc.backend
     own_rs_stream = cc.reduce_scatter_stream if cc.reduce_scatter_stream is not cc.all_gather_stream else torch.cuda.Stream(dev, priority=-1)
     for spec in a.configs.split(","):
-        flags = spec.split("+")[1:]
+        be.dry_run = spec == "dry"  # "dry": collectives move nothing, i.e. the compute-only step at this world size
+        if spec == "dry":
+            spec_run = "ce/sm"
+        else:
+            spec_run = spec
+        flags = spec_run.split("+")[1:]
         single, fused = "1s" in flags, "fr" in flags
-        body = spec.split("+")[0]
+        body = spec_run.split("+")[0]
         ag_s, rs_s = body.split("/")
         ag_p, rs_p = ag_s.split(":"), rs_s.split(":")
         ag, rs = ag_p[0], rs_p[0]

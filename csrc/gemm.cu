@@ -23,10 +23,11 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int GATHER_THREADS = 224;  // gather mode: one more warp, for the communication role
 
 // MODE_PLAIN: C is stored locally through TMA.  MODE_SCATTER: GEMM -> reduce-scatter, the fp32 rows of C are pushed to the
-// ranks that own them (see FusedArgs).
-constexpr int MODE_PLAIN = 0, MODE_SCATTER = 1;
+// ranks that own them.  MODE_GATHER: all-gather -> GEMM, the kernel also gathers the layer that B is part of (see FusedArgs).
+constexpr int MODE_PLAIN = 0, MODE_SCATTER = 1, MODE_GATHER = 2;
 constexpr int SCATTER_COLS = 64;                         // columns per pushed row piece: 256 bytes of fp32
 constexpr int SCATTER_PITCH = SCATTER_COLS * 4 + 16;     // row pitch of the staging block (16 B of padding: no bank conflicts)
 
@@ -36,10 +37,13 @@ struct GemmCfg {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   static constexpr int B_BYTES = B_ROWS * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (MODE == MODE_SCATTER) ? (STAGE_BYTES == 49152 ? 3 : 4) : ((STAGE_BYTES == 49152) ? 4 : 6);
+  static constexpr int RING_BYTES = (MODE == MODE_GATHER) ? 4 * 16384 : 0;  // the communication role's ring (COMM_SLOTS pieces)
+  static constexpr int STAGES = (MODE == MODE_SCATTER) ? (STAGE_BYTES == 49152 ? 3 : 4)
+                                : (MODE == MODE_GATHER) ? (STAGE_BYTES == 49152 ? 2 : (STAGE_BYTES == 32768 ? 4 : 5))
+                                                        : ((STAGE_BYTES == 49152) ? 4 : 6);
   static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
   // plain: two [128 rows x 128 B] swizzled blocks for TMA stores; scatter: two [128 rows x 256 B (+ padding)] linear blocks
-  static constexpr int STAGING_BYTES = (MODE == MODE_SCATTER) ? 2 * BLOCK_M * SCATTER_PITCH : 2 * 16384;
+  static constexpr int STAGING_BYTES = (MODE == MODE_SCATTER) ? 2 * BLOCK_M * SCATTER_PITCH : 2 * 16384 + RING_BYTES;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
 };
 
@@ -55,26 +59,27 @@ constexpr int MAX_RANKS = 16;
 
 // Arguments of the two fused compute + collective modes (both off when zero-initialised).
 //
-// gather (all-gather -> GEMM): the first `n_comm` CTAs of the grid are communication CTAs.  They pull every
-// rank's bf16 shard of the layer (peer loads over NVLink, local copy for the own shard) into the local layer
-// buffer chunk by chunk and publish a per-chunk flag; the GEMM CTAs' producer warp waits (bounded) for the
-// chunks that cover a B tile before it issues the TMA loads, so the GEMM runs while the rest of the layer
-// is still arriving, and the whole layer buffer is filled for the GEMMs that follow.
+// gather (all-gather -> GEMM, MODE_GATHER): every CTA of the GEMM carries one extra warp whose elected thread pulls its
+// share of every rank's bf16 shard of the layer (bulk loads from peer memory over NVLink into a small ring in shared
+// memory, bulk stores from there into the local layer buffer) and, for every piece that lies inside B, adds the piece's
+// bytes to the counter of the B column block it belongs to.  The producer warps wait (bounded) until the counter of a tile's
+// column block says that all of its rows have landed, then load B from the local buffer as usual.  The GEMM therefore
+// runs while the layer is still arriving, no SM is given up to communication, and when the kernel ends the whole layer
+// buffer is gathered for the GEMMs that follow.
 //
-// scatter (GEMM -> reduce-scatter): the fp32 epilogue does not store C locally; every 16-byte piece goes to the
-// rank that owns its position of the flat layer gradient, into that owner's staging slot for this rank
-// (slot r of the owner's reduce buffer = contributions of rank r to the owner's shard).  The owner then sums
-// its `world` slots locally in rank order.
+// scatter (GEMM -> reduce-scatter, MODE_SCATTER): the fp32 epilogue does not store C locally; every row piece goes to the
+// rank that owns its position of the flat layer gradient, into that owner's slot for this rank (slot r of the owner's
+// reduce buffer = contributions of rank r to the owner's shard).  The owner then sums its `world` slots locally in rank
+// order.
 struct FusedArgs {
   // gather
-  int n_comm;
+  int gather;
   int world, rank;
-  int chunks_per_shard;
-  unsigned int epoch;
-  unsigned int* flags;          // [world * chunks_per_shard], device memory of this GPU
+  unsigned long long* counters;      // [number of B column blocks] bytes landed, monotonic over calls (device memory of this GPU)
+  unsigned long long epoch;          // this call completes a block when its counter reaches epoch * bytes of the block
   const void* peer_in[MAX_RANKS];
   uint8_t* layer_buf;
-  long long shard_bytes, chunk_bytes, b_byte_off;
+  long long shard_bytes, b_byte_off;
   // optional: sum of squares of the (alpha-scaled) fp32 output, atomically added to *sumsq (gradient-norm fusion)
   float* sumsq;
   // scatter
@@ -83,24 +88,15 @@ struct FusedArgs {
   long long c_flat_off, shard_numel;
 };
 
-YF_DEVINL void st_release_gpu_u32(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-YF_DEVINL unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+YF_DEVINL unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+YF_DEVINL void red_add_release_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 YF_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
-
-// Communication role of the gather mode.  One thread per communication CTA drives the TMA unit: bulk loads
-// (cp.async.bulk, no multicast) bring 16 KB pieces of a peer's shard into a ring in this CTA's shared memory and bulk
-// stores write them to the local layer buffer, several pieces in flight in both directions, so a handful of CTAs keep
-// NVLink busy without spending registers or issue slots on the copy.  Chunk ids are (shard, chunk in shard); the chunks
-// that cover B come first (rotated by rank so that the ranks do not all read the same owner at once), then the rest.
-constexpr int COMM_PIECE = 16384;
-constexpr int COMM_NBUF = 12;       // 192 KB ring
-constexpr int COMM_LOOKAHEAD = 6;   // loads issued this many pieces ahead of the stores
 
 YF_DEVINL void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
@@ -112,107 +108,79 @@ YF_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
                "r"(smem_u32(smem_src)), "r"(bytes)
                : "memory");
 }
+YF_DEVINL void tma_store_wait1() { asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); }
 
-__device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, uint8_t* ring, uint64_t* ring_bars) {
-  if (threadIdx.x != 0) return;
-  for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&ring_bars[i], 1);
-  mbar_fence_init();
-  const int cps = fa.chunks_per_shard;
-  const int total = fa.world * cps;
-  auto chunk_of = [&](long long byte_off) {
-    const long long r = byte_off / fa.shard_bytes;
-    const long long j = (byte_off - r * fa.shard_bytes) / fa.chunk_bytes;
-    return (int)(r * cps + j);
+// Communication role of the gather mode: ONE thread of every CTA.  Piece q of the layer (q = 0, 1, ...) is piece q / world
+// of the shard of rank (rank + q % world) % world, so consecutive pieces come from different owners and, at any moment, the
+// ranks read from different peers; CTA c moves the pieces c, c + grid, c + 2 grid, ...  A piece goes peer -> ring slot
+// (bulk load, completion on an mbarrier) -> local layer buffer (bulk store); two loads and two stores are in flight.
+constexpr int COMM_PIECE = 16384;
+constexpr int COMM_SLOTS = 4;
+
+__device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long long block_bytes, uint8_t* ring, uint64_t* ring_bars) {
+  const long long pps = (fa.shard_bytes + COMM_PIECE - 1) / COMM_PIECE;  // pieces per shard
+  const long long total = pps * fa.world;
+  const long long first = blockIdx.x, step = gridDim.x;
+  const long long mine = first < total ? (total - first + step - 1) / step : 0;
+  auto piece = [&](long long i, const uint8_t*& src, long long& layer_off, uint32_t& bytes) {
+    const long long q = first + i * step;
+    const int owner = (fa.rank + (int)(q % fa.world)) % fa.world;
+    const long long lo = (q / fa.world) * COMM_PIECE;
+    bytes = (uint32_t)min((long long)COMM_PIECE, fa.shard_bytes - lo);
+    src = reinterpret_cast<const uint8_t*>(fa.peer_in[owner]) + lo;
+    layer_off = (long long)owner * fa.shard_bytes + lo;
   };
-  const int first = chunk_of(fa.b_byte_off);
-  const int last = chunk_of(fa.b_byte_off + b_bytes - 1);
-  const int nprio = last - first + 1;
-  const int rot = (int)(((long long)fa.rank * nprio) / fa.world);
-  auto chunk_id = [&](int q) {
-    if (q < nprio) return first + (q + rot) % nprio;
-    return (q - nprio < first) ? (q - nprio) : q;
+  auto issue_load = [&](long long i) {
+    const uint8_t* src; long long off; uint32_t bytes;
+    piece(i, src, off, bytes);
+    const int slot = (int)(i % COMM_SLOTS);
+    mbar_expect_tx(&ring_bars[slot], bytes);
+    bulk_load(ring + slot * COMM_PIECE, src, bytes, &ring_bars[slot]);
   };
-  // iterate pieces of this CTA's chunks through a two-cursor software pipeline: `ld` issues loads, `st` (COMM_LOOKAHEAD
-  // pieces behind) waits for a piece and stores it
-  struct Cursor {
-    int q;            // position in this CTA's chunk sequence
-    long long off;    // byte offset inside the chunk
-  };
-  Cursor ld{(int)blockIdx.x, 0}, st{(int)blockIdx.x, 0};
-  auto chunk_range = [&](int q, const uint8_t*& src, uint8_t*& dst, long long& bytes, int& id) {
-    id = chunk_id(q);
-    const int r = id / cps, j = id - r * cps;
-    const long long lo = (long long)j * fa.chunk_bytes;
-    const long long hi = min(lo + fa.chunk_bytes, fa.shard_bytes);
-    bytes = hi > lo ? hi - lo : 0;
-    src = reinterpret_cast<const uint8_t*>(fa.peer_in[r]) + lo;
-    dst = fa.layer_buf + (long long)r * fa.shard_bytes + lo;
-  };
-  uint32_t n_ld = 0, n_st = 0;
-  bool alive = true;
-  while (alive && st.q < total) {
-    // ---- issue the next load (if any piece is left and the ring slot is free)
-    if (ld.q < total && n_ld < n_st + COMM_LOOKAHEAD) {
-      const uint8_t* src; uint8_t* dst; long long bytes; int id;
-      chunk_range(ld.q, src, dst, bytes, id);
-      if (bytes == 0) { ld.q += fa.n_comm; ld.off = 0; continue; }
-      const uint32_t piece = (uint32_t)min((long long)COMM_PIECE, bytes - ld.off);
-      const int slot = n_ld % COMM_NBUF;
-      // the store that last read this slot (piece n_ld - COMM_NBUF) must have finished reading shared memory; stores are
-      // committed in order, so at most COMM_NBUF - COMM_LOOKAHEAD - 1 younger ones may still be pending
-      if (n_ld >= COMM_NBUF) asm volatile("cp.async.bulk.wait_group.read 5;" ::: "memory");
-      mbar_expect_tx(&ring_bars[slot], piece);
-      bulk_load(ring + slot * COMM_PIECE, src + ld.off, piece, &ring_bars[slot]);
-      ++n_ld;
-      ld.off += piece;
-      if (ld.off >= bytes) { ld.q += fa.n_comm; ld.off = 0; }
-      continue;
+  // piece i has been written to the layer buffer: credit the B column blocks it overlaps
+  auto publish = [&](long long i) {
+    const uint8_t* src; long long off; uint32_t bytes;
+    piece(i, src, off, bytes);
+    long long lo = max(off, fa.b_byte_off) - fa.b_byte_off, hi = min(off + (long long)bytes, fa.b_byte_off + b_bytes) - fa.b_byte_off;
+    if (lo >= hi) return;
+    fence_proxy_async_global();  // the bulk stores went through the async proxy; the counter is a generic-proxy access
+    while (lo < hi) {
+      const long long blk = lo / block_bytes;
+      const long long end = min(hi, (blk + 1) * block_bytes);
+      red_add_release_gpu_u64(fa.counters + blk, (unsigned long long)(end - lo));
+      lo = end;
     }
-    // ---- store the oldest loaded piece
-    const uint8_t* src; uint8_t* dst; long long bytes; int id;
-    chunk_range(st.q, src, dst, bytes, id);
-    if (bytes == 0) {
-      __threadfence();
-      st_release_gpu_u32(fa.flags + id, fa.epoch);
-      st.q += fa.n_comm; st.off = 0;
-      continue;
-    }
-    const uint32_t piece = (uint32_t)min((long long)COMM_PIECE, bytes - st.off);
-    const int slot = n_st % COMM_NBUF;
-    if (!mbar_wait(&ring_bars[slot], (n_st / COMM_NBUF) & 1, 12)) { alive = false; break; }
-    bulk_store(dst + st.off, ring + slot * COMM_PIECE, piece);
+  };
+  if (mine > 0) issue_load(0);
+  if (mine > 1) issue_load(1);
+  long long done = 0, stored = 0;  // pieces published / pieces whose store has been issued
+  for (long long i = 0; i < mine; ++i, ++stored) {
+    const int slot = (int)(i % COMM_SLOTS);
+    if (!mbar_wait(&ring_bars[slot], (uint32_t)((i / COMM_SLOTS) & 1), 12)) break;  // gave up: nothing more is copied or published
+    const uint8_t* src; long long off; uint32_t bytes;
+    piece(i, src, off, bytes);
+    bulk_store(fa.layer_buf + off, ring + slot * COMM_PIECE, bytes);
     tma_store_commit();
-    ++n_st;
-    st.off += piece;
-    if (st.off >= bytes) {
-      // chunk complete: its bytes must be in global memory before the flag says so
-      tma_store_wait0();
-      fence_proxy_async_global();
-      __threadfence();
-      st_release_gpu_u32(fa.flags + id, fa.epoch);
-      st.q += fa.n_comm; st.off = 0;
-    }
+    tma_store_wait_read1();  // every store but this one has finished reading its slot: the slot of piece i - 2 is free
+    if (i + 2 < mine) issue_load(i + 2);
+    tma_store_wait1();       // every store but this one has completed: piece i - 1 is in the layer buffer
+    if (i >= 1) { publish(i - 1); done = i; }
   }
   tma_store_wait0();
+  for (long long i = done; i < stored; ++i) publish(i);
 }
 
 template <int BLOCK_N, int CG, int MODE>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(MODE == MODE_GATHER ? GATHER_THREADS : GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
   using Cfg = GemmCfg<BLOCK_N, CG, MODE>;
-  if (CG == 1 && fa.n_comm > 0 && (int)blockIdx.x < fa.n_comm) {
-    extern __shared__ uint8_t comm_smem_raw[];
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 1023) & ~uintptr_t(1023));
-    gather_comm_role(fa, (long long)args.N * args.K * 2, ring, reinterpret_cast<uint64_t*>(ring + COMM_NBUF * COMM_PIECE));
-    return;
-  }
   // CG == 2: the grid is a sequence of CTA pairs (clusters of two); a pair works on one 256 x BLOCK_N tile, CTA `crank` of
   // the pair on its rows [crank * 128, +128) with the B rows [crank * BLOCK_N / 2, +BLOCK_N / 2) in its shared memory
   const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u;
   const bool leader = crank == 0;
-  const int unit = ((int)blockIdx.x - fa.n_comm) / CG;        // index among the tile workers (CTAs or pairs)
-  const int nunits = ((int)gridDim.x - fa.n_comm) / CG;
+  const int unit = (int)blockIdx.x / CG;        // index among the tile workers (CTAs or pairs)
+  const int nunits = (int)gridDim.x / CG;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int TILE_M = BLOCK_M * CG;
   constexpr int B_ROWS = Cfg::B_ROWS;
@@ -225,6 +193,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   uint64_t* tfull = bars + 2 * STAGES;   // [2]
   uint64_t* tempty = tfull + 2;          // [2]       (pairs: only the leader's are used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* ring_bars = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // [COMM_SLOTS], gather mode
+  uint8_t* ring = staging + Cfg::STAGING_BYTES - Cfg::RING_BYTES;     // gather mode: the tail of the staging area
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -247,6 +217,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
     }
+    if (MODE == MODE_GATHER)
+      for (int i = 0; i < COMM_SLOTS; ++i) mbar_init(&ring_bars[i], 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -282,28 +254,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       for (int t = unit; t < num_tiles && alive; t += nunits) {
         int m0, n0;
         tile_coords(t, m0, n0);
-        if (CG == 1 && fa.n_comm > 0) {
-          // gather mode: the rows [n0, n0 + BLOCK_N) of B must have landed in the local layer buffer
-          const long long lo = fa.b_byte_off + (long long)n0 * K * 2;
-          const long long hi = fa.b_byte_off + (long long)min(n0 + BLOCK_N, N) * K * 2 - 1;
-          const long long r_lo = lo / fa.shard_bytes, r_hi = hi / fa.shard_bytes;
-          const int c_lo = (int)(r_lo * fa.chunks_per_shard + (lo - r_lo * fa.shard_bytes) / fa.chunk_bytes);
-          const int c_hi = (int)(r_hi * fa.chunks_per_shard + (hi - r_hi * fa.shard_bytes) / fa.chunk_bytes);
+        if (MODE == MODE_GATHER) {
+          // the rows [n0, n0 + BLOCK_N) of B must have landed in the local layer buffer: the column block's counter says so
+          const int blk = n0 / BLOCK_N;
+          const unsigned long long want = fa.epoch * (unsigned long long)((long long)min(BLOCK_N, N - n0) * K * 2);
           const uint64_t t0 = yf_globaltimer();
-          for (int c = c_lo; c <= c_hi && alive; ++c) {
-            for (uint32_t spin = 0; ld_acquire_gpu_u32(fa.flags + c) != fa.epoch; ++spin) {
-              if ((spin & 63u) == 63u) {
-                if (yf_aborted() || yf_globaltimer() - t0 > YF_WAIT_NS_DEFAULT) {
-                  yf_raise(YF_ERR_FLAG_TIMEOUT, 11);
-                  alive = false;
-                  break;
-                }
-                __nanosleep(100);
+          for (uint32_t spin = 0; ld_acquire_gpu_u64(fa.counters + blk) < want; ++spin) {
+            if ((spin & 63u) == 63u) {
+              if (yf_aborted() || yf_globaltimer() - t0 > YF_WAIT_NS_DEFAULT) {
+                yf_raise(YF_ERR_FLAG_TIMEOUT, 11);
+                alive = false;
+                break;
               }
+              __nanosleep(100);
             }
           }
           if (!alive) break;
-          fence_proxy_async_global();  // the chunks were written with generic stores; TMA reads them through the async proxy
+          fence_proxy_async_global();  // the rows were written by other CTAs; TMA reads them through the async proxy
         }
         const int nb = n0 + (int)crank * B_ROWS;  // first B row this CTA holds
         for (int kb = 0; kb < num_k; ++kb, ++it) {
@@ -401,6 +368,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
       }
     }
+  } else if (MODE == MODE_GATHER && warp == 6) {
+    // ------------------------------------------------------------ communication role (gather mode)
+    if (lane == 0) gather_comm_role(fa, (long long)N * K * 2, (long long)BLOCK_N * K * 2, ring, ring_bars);
   } else {
     // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
     // TMEM -> registers -> 128-byte-swizzled staging block in shared memory -> TMA store (or TMA
@@ -579,15 +549,16 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedA
   const int num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
   int sms = yf_num_sms();
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
-  int units = (sms - fa.n_comm) / CG;
+  int units = sms / CG;
   if (units < 1) return -1;
-  if (num_tiles < units) units = num_tiles;
-  // never more CTAs than SMs: the communication CTAs and the GEMM CTAs that wait on them are co-resident
-  const int grid = units * CG + fa.n_comm;
+  // never more CTAs than SMs (producers may wait on other CTAs' communication warps: all of them must be resident); the
+  // gather mode keeps every SM's communication warp even when the GEMM has fewer tiles than that
+  if (num_tiles < units && MODE != MODE_GATHER) units = num_tiles;
+  const int grid = units * CG;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.blockDim = dim3(MODE == MODE_GATHER ? GATHER_THREADS : GEMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -608,12 +579,16 @@ int dispatch_gemm(const void* A, const void* B, const GemmArgs& args, const Fuse
                   cudaStream_t s) {
   const int M = args.M, N = args.N;
   const bool use256 = (N >= 256) && ((N % 256 == 0) || (N % 256 > 128) || N >= 2048);
-  const bool fused = fa.n_comm > 0;
   static const int force_cg = [] {
     const char* v = getenv("YAFSDP_GEMM_CTA_GROUP");
     return v ? atoi(v) : 0;
   }();
-  const bool pair_ok = !fused && use256 && M >= 256 && (M % 256 == 0 || M % 256 > 128 || M >= 2048);
+  const bool pair_ok = use256 && M >= 256 && (M % 256 == 0 || M % 256 > 128 || M >= 2048);
+  if (fa.gather) {
+    if (pair_ok && force_cg != 1) return launch_gemm<256, 2, MODE_GATHER>(A, B, args, fa, lda, ldb, sm_limit, s);
+    return use256 ? launch_gemm<256, 1, MODE_GATHER>(A, B, args, fa, lda, ldb, sm_limit, s)
+                  : launch_gemm<128, 1, MODE_GATHER>(A, B, args, fa, lda, ldb, sm_limit, s);
+  }
   if (fa.scatter) {
     if (pair_ok && force_cg != 1) return launch_gemm<256, 2, MODE_SCATTER>(A, B, args, fa, lda, ldb, sm_limit, s);
     return use256 ? launch_gemm<256, 1, MODE_SCATTER>(A, B, args, fa, lda, ldb, sm_limit, s)
@@ -667,23 +642,23 @@ extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, 
 }
 
 // All-gather -> GEMM in one kernel.  C[M,N] = A[M,K] * B[N,K]^T where B (row-major, contiguous, K-major) is a
-// sub-range of the layer's flat bf16 parameter buffer that is being gathered by the same kernel:
+// sub-range of the layer's flat bf16 parameter buffer that the same kernel gathers:
 //   peer_in[r]  : rank r's shard (shard_bytes bytes) of the layer, peer-mapped; entry `rank` is the local shard
 //   layer_buf   : local unsharded layer buffer (world * shard_bytes bytes); B = layer_buf + b_byte_off
-//   flags/epoch : world * chunks_per_shard words of this GPU's memory; a chunk is ready when its word == epoch
-//                 (use a new epoch for every call on the same flags, never 0)
-//   n_comm      : CTAs that copy (the GEMM gets the remaining SMs)
+//   counters    : one unsigned 64-bit word per B column block of 256 rows (128 when N < 256), in this GPU's memory, zero
+//                 before the first call; epoch = 1, 2, ... counts the calls made with these counters and this shape
 // On return (stream order) the whole layer buffer is filled, not only B.
 extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int a_mn,
                                      int out_f32, void* const* peer_in, void* layer_buf, long long shard_bytes,
-                                     long long b_byte_off, int rank, int world, void* flags, unsigned int epoch,
-                                     long long chunk_bytes, int n_comm, void* stream) {
+                                     long long b_byte_off, int rank, int world, void* counters, long long epoch, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
-  if ((lda % 8) || (K % 8) || (ldc % (out_f32 ? 4 : 8)) || n_comm < 1 || epoch == 0) return -1;
-  if ((shard_bytes % 16) || (chunk_bytes % 16) || chunk_bytes <= 0 || (b_byte_off % 16)) return -1;
+  if ((lda % 8) || (K % 8) || (ldc % (out_f32 ? 4 : 8)) || epoch <= 0 || counters == nullptr) return -1;
+  if ((shard_bytes % 16) || shard_bytes <= 0 || (b_byte_off % 16)) return -1;
   if (b_byte_off < 0 || b_byte_off + (long long)N * K * 2 > shard_bytes * world) return -1;
   const uint8_t* B = reinterpret_cast<const uint8_t*>(layer_buf) + b_byte_off;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(layer_buf)) & 15)
+    return -1;
   GemmArgs args;
   args.C = C;
   args.M = M; args.N = N; args.K = K;
@@ -695,12 +670,10 @@ extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K
   args.accumulate = 0;
   FusedArgs fa;
   memset(&fa, 0, sizeof(fa));
-  fa.n_comm = n_comm;
+  fa.gather = 1;
   fa.world = world; fa.rank = rank;
-  fa.chunk_bytes = chunk_bytes;
-  fa.chunks_per_shard = (int)((shard_bytes + chunk_bytes - 1) / chunk_bytes);
-  fa.epoch = epoch;
-  fa.flags = reinterpret_cast<unsigned int*>(flags);
+  fa.counters = reinterpret_cast<unsigned long long*>(counters);
+  fa.epoch = (unsigned long long)epoch;
   for (int r = 0; r < world; ++r) {
     if (!peer_in[r] || (reinterpret_cast<uintptr_t>(peer_in[r]) & 15)) return -1;
     fa.peer_in[r] = peer_in[r];

@@ -24,7 +24,7 @@ int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, int N, int 
 // fused all-gather -> GEMM and GEMM -> reduce-scatter (same kernel, see gemm.cu for the argument contracts)
 int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int a_mn, int out_f32,
                           void* const* peer_in, void* layer_buf, long long shard_bytes, long long b_byte_off, int rank, int world,
-                          void* flags, unsigned int epoch, long long chunk_bytes, int n_comm, void* stream);
+                          void* counters, long long epoch, void* stream);
 int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int a_mn, int b_mn,
                          float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel, int rank, int world,
                          int sm_limit, void* stream);

@@ -157,14 +157,14 @@ def _fused_worker(rank, world):
     inp = be.alloc(shard, torch.bfloat16, dev, "gather_input")
     inp.copy_(full[rank * shard : (rank + 1) * shard])
     layer_buf = torch.zeros(total, device=dev, dtype=torch.bfloat16)
-    flags = torch.zeros(4096, device=dev, dtype=torch.int32)
+    counters = torch.zeros((n + 127) // 128, device=dev, dtype=torch.int64)
     a = torch.randn(m, k, device=dev).bfloat16()
     torch.cuda.synchronize()
     be.step_barrier()
     for epoch in (1, 2):
         layer_buf.zero_()
         out = kernels.gemm_gathered(a, n, k, peer_in=be._peers(inp), layer_buf=layer_buf, shard_bytes=shard * 2, b_byte_off=head * 2,
-                                    rank=rank, world=world, flags=flags, epoch=epoch, chunk_bytes=64 * 1024, n_comm=8)
+                                    rank=rank, world=world, counters=counters, epoch=epoch)
         torch.cuda.synchronize()
         assert torch.equal(layer_buf, full), "layer buffer is not the all-gather of the shards"
         ref = a.float() @ full[head : head + n * k].view(n, k).float().t()
@@ -182,15 +182,15 @@ def _fused_worker(rank, world):
     gbuf.zero_()
     torch.cuda.synchronize()
     be.barrier(3)
+    gbuf.fill_(float("nan"))  # whatever the pushes and the padding rule do not cover would poison the sums
+    be.barrier(3)
     kernels.gemm_scatter(dy, x, a_mn_major=True, b_mn_major=True, peer_grad=be._peers(gbuf), c_flat_off=flat_off, shard_numel=pshard,
                          rank=rank, world=world)
-    be.barrier(3)  # everybody's pushes have landed
-    base = gbuf.data_ptr()
-    local_slots = _ptr_array([base + (r - rank) * pshard * 4 for r in range(world)])  # the pull kernel adds rank * shard
+    kernels.push_flat(None, flat_off, 0, be._peers(gbuf), pshard, rank, world)  # the range in front of the matrix: zeros
+    tail0 = flat_off + rows * cols
+    kernels.push_flat(torch.zeros(8 * 5, device=dev), 8 * 5, tail0, be._peers(gbuf), pshard, rank, world)
     got = torch.zeros(pshard, device=dev, dtype=torch.float32)
-    rc = kernels._native.lib().yf_reduce_scatter_pull(local_slots, got.data_ptr(), pshard, rank, world, 1.0 / world, 0, 0, 0,
-                                                      torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
+    be.reduce_pushed(got, gbuf, scale=1.0 / world, accumulate=False, valid_numel=tail0 + 8 * 5)  # waits for everybody's pushes
     local_dw = torch.zeros(ptotal, device=dev, dtype=torch.float32)
     local_dw[flat_off : flat_off + rows * cols] = (dy.float().t() @ x.float()).reshape(-1)
     want = torch.empty(pshard, device=dev, dtype=torch.float32)

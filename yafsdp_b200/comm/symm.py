@@ -227,6 +227,9 @@ class SymmBackend(CommBackend):
         self._int_ptr_cache: dict[int, list[int]] = {}
         # reduce buffers that peers may still be reading: data pointer -> sequence number of the reduce-scatter
         self._unread: dict[int, int] = {}
+        # measurement aid: collectives move nothing between GPUs (gathers are skipped, reductions only read the own chunk),
+        # so a step timed with it is the compute-only step at this world size; the numbers it trains on are meaningless
+        self.dry_run = False
         self.ag_transport = self.rs_transport = "ce"
         self.set_transports(ag, rs, warn=True)
         torch.cuda.synchronize(device)
@@ -291,7 +294,8 @@ class SymmBackend(CommBackend):
         self._pad(slot, self._seq[slot], 3)
 
     def step_barrier(self) -> None:
-        self.barrier(self.SLOT_STEP)
+        if not self.dry_run:
+            self.barrier(self.SLOT_STEP)
 
     def before_write(self, buf: torch.Tensor) -> None:
         """``buf`` (a reduce input of an earlier :meth:`reduce_scatter`) is about to be overwritten on the current stream:
@@ -329,7 +333,18 @@ class SymmBackend(CommBackend):
         kernels._launches += len(copies)
 
     # ------------------------------------------------------------------ collectives
+    def _reduce_own_chunk(self, dst: torch.Tensor, inp: torch.Tensor, shard: int, scale: float, accumulate: bool,
+                          sumsq: torch.Tensor | None) -> bool:
+        own = _ptr_array([inp.data_ptr() + self.rank * shard * inp.element_size()])
+        rc = _native.lib().yf_reduce_scatter_pull_sumsq(own, dst.data_ptr(), shard, 0, 1, float(scale), int(accumulate),
+                                                        int(inp.dtype == torch.bfloat16), self.rs_ctas,
+                                                        None if sumsq is None else sumsq.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        kernels._check(rc, "yf_reduce_scatter_pull")
+        return sumsq is not None
+
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
+        if self.dry_run:
+            return
         nbytes = inp.numel() * inp.element_size()
         mc_out = self.arena.mc_ptr(out) if self.ag_transport == "mc" else 0
         if mc_out:
@@ -357,6 +372,8 @@ class SymmBackend(CommBackend):
         if dst.dtype != torch.float32 or inp.dtype not in (torch.float32, torch.bfloat16):
             raise NotImplementedError("the symmetric reduce-scatter produces fp32 from an fp32 or bf16 wire format")
         shard = inp.numel() // self.world
+        if self.dry_run:
+            return self._reduce_own_chunk(dst, inp, shard, scale, accumulate, sumsq)
         self.barrier(self.SLOT_RS_READY)  # every rank's gradients for this group are complete
         seq = self._seq[self.SLOT_RS_READY]
         stream = torch.cuda.current_stream().cuda_stream
@@ -410,6 +427,8 @@ class SymmBackend(CommBackend):
         if dst.dtype != torch.float32 or slots.dtype != torch.float32:
             raise NotImplementedError("pushed gradients are fp32")
         shard = slots.numel() // self.world
+        if self.dry_run:
+            return self._reduce_own_chunk(dst, slots, shard, scale, accumulate, sumsq)
         self.barrier(self.SLOT_RS_READY)  # every rank's pushes for this group have completed
         seq = self._seq[self.SLOT_RS_READY]
         if valid_numel is not None:

@@ -115,19 +115,19 @@ def gemm(
 
 
 def gemm_gathered(a: torch.Tensor, n: int, k: int, *, peer_in: Any, layer_buf: torch.Tensor, shard_bytes: int, b_byte_off: int,
-                  rank: int, world: int, flags: torch.Tensor, epoch: int, chunk_bytes: int = 1 << 20, n_comm: int = 16,
-                  out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, a_mn_major: bool = False) -> torch.Tensor:
+                  rank: int, world: int, counters: torch.Tensor, epoch: int, out: torch.Tensor | None = None,
+                  out_dtype: torch.dtype = torch.bfloat16, a_mn_major: bool = False) -> torch.Tensor:
     """All-gather -> GEMM in one kernel: ``out = A @ B^T`` where ``B [n, k]`` (bf16, contiguous) starts ``b_byte_off`` bytes
     into ``layer_buf``, which the same kernel fills from every rank's shard (``peer_in``: ctypes array of ``world`` peer
-    pointers).  ``flags``: int32 tensor with one word per chunk; pass a fresh non-zero ``epoch`` per call."""
+    pointers).  ``counters``: int64 tensor with one word per 256-row block of ``B``, zero before the first call;
+    ``epoch`` = 1, 2, ... counts the calls made with these counters."""
     m = a.shape[1] if a_mn_major else a.shape[0]
     if out is None:
         out = torch.empty((m, n), device=a.device, dtype=out_dtype)
-    cps = (shard_bytes + chunk_bytes - 1) // chunk_bytes
-    assert flags.dtype == torch.int32 and flags.numel() >= world * cps
+    assert counters.dtype == torch.int64 and counters.numel() >= (n + 127) // 128 and epoch >= 1
     rc = _native.lib().yf_gemm_bf16_gathered(
         a.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), out.stride(0), int(a_mn_major), int(out.dtype == torch.float32),
-        peer_in, layer_buf.data_ptr(), shard_bytes, b_byte_off, rank, world, flags.data_ptr(), epoch, chunk_bytes, n_comm, _stream())
+        peer_in, layer_buf.data_ptr(), shard_bytes, b_byte_off, rank, world, counters.data_ptr(), epoch, _stream())
     _check(rc, "yf_gemm_bf16_gathered")
     return out
 

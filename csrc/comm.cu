@@ -244,6 +244,12 @@ __global__ void __launch_bounds__(256) push_flat_kernel(const float4* __restrict
     const long long f = flat_off + i * 4;
     const long long o = f / shard_numel;
     const long long loc = f - o * shard_numel;
+#ifdef YF_DEBUG_BOUNDS
+    if (o < 0 || o >= MAX_RANKS || peer_grad.p[o] == nullptr || loc + 4 > shard_numel) {  // debug build: record and skip
+      yf_raise(YF_ERR_BAD_ARGUMENT, 41);
+      continue;
+    }
+#endif
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(peer_grad.p[o]) + (long long)rank * shard_numel + loc) = v;
   }
 }

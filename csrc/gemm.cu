@@ -143,7 +143,9 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long lo
     piece(i, src, off, bytes);
     long long lo = max(off, fa.b_byte_off) - fa.b_byte_off, hi = min(off + (long long)bytes, fa.b_byte_off + b_bytes) - fa.b_byte_off;
     if (lo >= hi) return;
-    fence_proxy_async_global();  // the bulk stores went through the async proxy; the counter is a generic-proxy access
+    // The piece's bulk store has completed (wait_group), so its bytes are in global memory; the release below orders them
+    // before the counter.  No proxy fence here: it would wait for every asynchronous operation this CTA has in flight (the
+    // GEMM's own loads and MMAs included) once per piece; the reader fences once per tile instead.
     while (lo < hi) {
       const long long blk = lo / block_bytes;
       const long long end = min(hi, (blk + 1) * block_bytes);
@@ -154,18 +156,34 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long lo
   if (mine > 0) issue_load(0);
   if (mine > 1) issue_load(1);
   long long done = 0, stored = 0;  // pieces published / pieces whose store has been issued
+#ifdef YF_GATHER_PROFILE
+  unsigned long long tp[5] = {0, 0, 0, 0, 0};
+  unsigned long long t_a = yf_globaltimer(), t_b;
+#define YF_TICK(k) t_b = yf_globaltimer(); tp[k] += t_b - t_a; t_a = t_b;
+#else
+#define YF_TICK(k)
+#endif
   for (long long i = 0; i < mine; ++i, ++stored) {
     const int slot = (int)(i % COMM_SLOTS);
     if (!mbar_wait(&ring_bars[slot], (uint32_t)((i / COMM_SLOTS) & 1), 12)) break;  // gave up: nothing more is copied or published
+    YF_TICK(0)
     const uint8_t* src; long long off; uint32_t bytes;
     piece(i, src, off, bytes);
     bulk_store(fa.layer_buf + off, ring + slot * COMM_PIECE, bytes);
     tma_store_commit();
     tma_store_wait_read1();  // every store but this one has finished reading its slot: the slot of piece i - 2 is free
+    YF_TICK(1)
     if (i + 2 < mine) issue_load(i + 2);
+    YF_TICK(2)
     tma_store_wait1();       // every store but this one has completed: piece i - 1 is in the layer buffer
+    YF_TICK(3)
     if (i >= 1) { publish(i - 1); done = i; }
+    YF_TICK(4)
   }
+#ifdef YF_GATHER_PROFILE
+  for (int k = 0; k < 5; ++k) fa.counters[1024 + 8 * blockIdx.x + k] = tp[k];
+  fa.counters[1024 + 8 * blockIdx.x + 5] = (unsigned long long)mine;
+#endif
   tma_store_wait0();
   for (long long i = done; i < stored; ++i) publish(i);
 }
@@ -434,6 +452,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             const long long o = f / fa.shard_numel;                       // owner rank
             const long long loc = f - o * fa.shard_numel;
             const long long first = min(ncols, fa.shard_numel - loc);
+#ifdef YF_DEBUG_BOUNDS
+            // debug build: a piece that would leave the owners' slots is recorded and skipped instead of stored
+            if (f < 0 || o >= fa.world || (first < ncols && o + 1 >= fa.world) || loc < 0 || (first & 3) || (loc & 3)) {
+              yf_raise(YF_ERR_BAD_ARGUMENT, 40);
+              tma_store_commit();
+              continue;
+            }
+#endif
             float* dst = reinterpret_cast<float*>(fa.peer_grad[o]) + (long long)fa.rank * fa.shard_numel + loc;
             bulk_store(dst, srow, (uint32_t)(first * 4));
             if (first < ncols) {

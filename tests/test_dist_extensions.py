@@ -129,3 +129,87 @@ def test_all_gather_extension_int8():
 @pytest.mark.timeout(180)
 def test_extension_and_ordinary_parameters_in_one_module():
     run_distributed(_mixed_worker, 2)
+
+
+class ScaledWeight(torch.Tensor):
+    """Wrapper tensor subclass (inner tensors, ``__tensor_flatten__``): fp32 values in ``_data`` plus a per-tensor
+    ``_scale``; travels as int8 like ``Int8Weight``.  Only what sharding needs is dispatched: detach, new_zeros, to."""
+
+    @staticmethod
+    def __new__(cls, data, scale):
+        return torch.Tensor._make_wrapper_subclass(cls, data.shape, dtype=data.dtype, device=data.device, requires_grad=False)
+
+    def __init__(self, data, scale):
+        self._data = data
+        self._scale = scale
+
+    def __tensor_flatten__(self):
+        return ["_data", "_scale"], None
+
+    @staticmethod
+    def __tensor_unflatten__(inner, meta, outer_size, outer_stride):
+        return ScaledWeight(inner["_data"], inner["_scale"])
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        self = args[0]
+        if func in (aten.detach.default, aten.alias.default):
+            return ScaledWeight(self._data.detach(), self._scale)
+        if func is aten.new_zeros.default:
+            return ScaledWeight(self._data.new_zeros(*args[1:], **kwargs), self._scale)
+        if func in (aten._to_copy.default,):
+            return ScaledWeight(func(self._data, *args[1:], **kwargs), self._scale)
+        raise NotImplementedError(f"ScaledWeight: {func}")
+
+    __torch_function__ = torch._C._disabled_torch_function_impl
+
+    def fsdp_pre_all_gather(self, mesh):
+        q = torch.clamp(torch.round(self._data / self._scale), -127, 127).to(torch.int8)
+        return (q,), {"scale": self._scale}
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype, *, out=None):
+        (q,) = all_gather_outputs
+        deq = q.to(param_dtype) * metadata["scale"]
+        if out is not None:
+            out.copy_(deq)
+            return None
+        return deq, (q,)
+
+
+def _wrapper_worker(rank, world):
+    """A parameter whose tensor is a wrapper subclass with inner tensors: the hooks run on a local wrapper whose first
+    inner tensor is the master shard, so optimizer updates of the shard reach the next gather."""
+    from yafsdp_b200 import MixedPrecisionPolicy, RaggedShardDTensor, fully_shard
+
+    torch.manual_seed(0)
+    lin = nn.Linear(24, 16, bias=False)
+    full = lin.weight.detach().clone()
+    lin.weight = nn.Parameter(ScaledWeight(lin.weight.data.clone(), torch.tensor(SCALE)))
+    norm = nn.LayerNorm(24)
+    model = nn.Sequential(norm, lin)
+    policy = MixedPrecisionPolicy(all_gather_dtype_to_param_cls={torch.int8: ScaledWeight})
+    fully_shard(lin, mp_policy=policy)
+    fully_shard(norm)
+    fully_shard(model)
+    g = lin._get_fsdp_state()._param_group
+    assert g.all_gather_dtype == torch.int8 and isinstance(lin.weight, RaggedShardDTensor)
+    x = torch.randn(4, 24, generator=torch.Generator().manual_seed(5 + rank))
+
+    def quantise(w):
+        return torch.clamp(torch.round(w / SCALE), -127, 127) * SCALE
+
+    out = model(x)
+    assert torch.allclose(out, nn.functional.linear(nn.functional.layer_norm(x, (24,)), quantise(full)), atol=1e-5)
+    out.sum().backward()
+    assert isinstance(lin.weight.grad, RaggedShardDTensor)
+    with torch.no_grad():
+        lin.weight._local_tensor.add_(0.25)  # what an optimizer does: the wrapper's inner tensor sees it
+    out2 = model(x)
+    assert torch.allclose(out2, nn.functional.linear(nn.functional.layer_norm(x, (24,)), quantise(full + 0.25)), atol=1e-5)
+
+
+@pytest.mark.timeout(180)
+def test_wrapper_subclass_extension_parameter():
+    run_distributed(_wrapper_worker, 2)

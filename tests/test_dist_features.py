@@ -595,3 +595,73 @@ def _clip_variants_worker(rank, world):
 @pytest.mark.timeout(180)
 def test_torch_clipping_variants_on_sharded_grads():
     run_distributed(_clip_variants_worker, 3)
+
+
+# ------------------------------------------------------------------------------------------------
+def _apply_after_forward_worker(rank, world):
+    """``module.to(dtype)`` / ``.float()`` / ``.double()`` after the first forward: the sharded storage keeps its dtype and
+    takes over the transformed values (as the reference does), and training continues."""
+    model = _shard(_build())
+    opt = torch.optim.SGD(model.parameters(), lr=1e-2)
+    _loss(model, _data(rank)).backward()
+    opt.step()
+    before = {n: p.full_tensor().clone() for n, p in model.named_parameters()}
+    model.double()  # a no-op on the values; the parameters stay float32 RaggedShardDTensors bound to the same storage
+    for n, p in model.named_parameters():
+        assert p.dtype == torch.float32 and torch.equal(p.full_tensor(), before[n]), n
+    model.to(torch.bfloat16)  # values go through bfloat16 and come back rounded
+    for n, p in model.named_parameters():
+        assert p.dtype == torch.float32
+        assert torch.equal(p.full_tensor(), before[n].to(torch.bfloat16).float()), n
+    # the optimizer still holds the registered parameters and the next gather uses the new values
+    opt.zero_grad()
+    _loss(model, _data(rank)).backward()
+    opt.step()
+    ref = _build()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            p.copy_(before[n].to(torch.bfloat16).float())
+    ropt = torch.optim.SGD(ref.parameters(), lr=1e-2)
+    for r in range(world):
+        (_loss(ref, _data(r)) / world).backward()
+    ropt.step()
+    _check_params(model, {n: p.detach() for n, p in ref.named_parameters()})
+
+
+@pytest.mark.timeout(180)
+def test_module_apply_after_first_forward():
+    run_distributed(_apply_after_forward_worker, 2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _clip_with_plain_param_worker(rank, world):
+    """``clip_grad_norm_`` of this package with an ignored (replicated, unsharded) parameter beside sharded ones: the
+    plain gradient is whole on every rank and must enter the total once, not once per rank."""
+    from yafsdp_b200 import fully_shard
+    from yafsdp_b200.optim import clip_grad_norm_
+
+    ref = _build()
+    for r in range(world):
+        (_loss(ref, _data(r)) / world).backward()
+    want = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1e9)
+    model = _build()
+    ignored = {model.norm.weight, model.norm.bias}
+    fully_shard(model.emb)
+    for l in model.layers:
+        fully_shard(l)
+    fully_shard(model.head)
+    fully_shard(model, ignored_params=ignored)  # the root itself manages nothing: the norm's parameters stay plain
+    _loss(model, _data(rank)).backward()
+    # data-parallel average of the replicated parameters' gradients is the user's job
+    import torch.distributed as dist
+
+    for p in ignored:
+        dist.all_reduce(p.grad)
+        p.grad /= world
+    got = clip_grad_norm_(model, 1e9)
+    assert torch.allclose(got, want, rtol=1e-5), (got, want)
+
+
+@pytest.mark.timeout(180)
+def test_clip_grad_norm_counts_plain_gradients_once():
+    run_distributed(_clip_with_plain_param_worker, 2)

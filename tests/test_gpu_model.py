@@ -185,3 +185,35 @@ def test_micro_batch_accumulation_and_checkpointing_on_gpu():
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_fused_gradient_norm_with_micro_batches_on_gpu():
+    """The clipping norm that ShardedAdamW takes from the kernels' fused sums of squares equals the norm of the
+    accumulated gradients, also when a step has two micro-batches (every gradient is then written twice: the sums
+    taken by the first write are stale and a plain pass must replace them)."""
+    import torch.distributed as dist
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.ops import kernels
+    from yafsdp_b200.optim import ShardedAdamW, param_groups_of
+    from yafsdp_b200.train import build_llama
+
+    created = _single_rank_group()
+    try:
+        dev = torch.device("cuda", 0)
+        cfg = CONFIGS["tiny-gpu"]
+        ids = torch.randint(0, cfg.vocab_size, (4, 256), device=dev)
+        for batches in ([ids], [ids[:2], ids[2:]]):
+            model = build_llama(cfg, dev, seed=2)
+            opt = ShardedAdamW(model, lr=0.0, weight_decay=0.0, max_grad_norm=1e-3)  # lr 0: the step only measures the norm
+            for step in range(2):
+                opt.zero_grad()
+                for b in batches:
+                    (model(b, labels=b) / len(batches)).backward()
+                want = torch.sqrt(sum(g.sharded_grad_flat.double().pow(2).sum() for g in param_groups_of(model))).item()
+                opt.step()
+                got = opt.last_grad_norm.item()
+                assert abs(got - want) <= 2e-3 * want, (len(batches), step, got, want)
+        kernels.check_status()
+    finally:
+        if created:
+            dist.destroy_process_group()

@@ -35,6 +35,10 @@ NVCC_FLAGS = [
     "-fPIC",
 ]
 
+# extra compiler flags, e.g. ``-DYF_DEBUG_BOUNDS`` (the pushing kernels check every peer write against the owners' slots,
+# record a violation in the status word and skip the access); part of the rebuild digest
+NVCC_FLAGS += [f for f in os.environ.get("YAFSDP_NVCC_FLAGS", "").split() if f]
+
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None
 

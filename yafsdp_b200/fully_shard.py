@@ -98,6 +98,12 @@ def _move_states_to_device(params: list[nn.Parameter], buffers: list[torch.Tenso
             if isinstance(t, nn.Parameter):
                 continue
             t.data = torch.empty_like(t, device=device)
+        elif hasattr(t.data, "__tensor_flatten__"):
+            # wrapper tensor subclass (inner tensors): `.data =` would only move the outer shell, so swap the whole object
+            # (``ya_fsdp/_init.py:209-216``)
+            with torch.no_grad():
+                moved = nn.Parameter(t.to(device), requires_grad=t.requires_grad) if isinstance(t, nn.Parameter) else t.to(device)
+            torch.utils.swap_tensors(t, moved)
         else:
             t.data = t.data.to(device)
 

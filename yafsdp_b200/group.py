@@ -362,15 +362,28 @@ class ParamGroup:
                 pl = self.layout.placement(sp.index, self.rank)
                 sp.placement = pl
                 local = self._master[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                wrapper = sp.ext_cls is not None and hasattr(p.data, "__tensor_flatten__")
                 if pl.local_numel and p.device.type != "meta":
-                    src = _outer_local(p.detach()).reshape(-1)[pl.global_offset : pl.global_offset + pl.local_numel]
-                    local.copy_(src)
+                    # a wrapper subclass keeps its values in its first inner tensor: that is what the master shards
+                    full = getattr(p.data, p.data.__tensor_flatten__()[0][0]) if wrapper else _outer_local(p.detach())
+                    local.copy_(full.reshape(-1)[pl.global_offset : pl.global_offset + pl.local_numel])
                 spec = RaggedSpec(
                     mesh, (RaggedShard(pl.local_numel, pl.global_offset, pl.shard_numels),), torch.Size(sp.orig_shape),
                     _contiguous_stride(sp.orig_shape), self.orig_dtype, sp.outer_mesh, sp.outer_placements, sp.outer_shape,
                 )
                 sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
-                if sp.ext_cls is not None:
+                if wrapper:
+                    # the hooks are called on a wrapper of the local size whose first inner tensor IS the master slice
+                    # (``ya_fsdp/_param.py:146-155``); its other inner tensors (scales, ...) are whatever new_zeros gives them
+                    shell = p.data.new_zeros(pl.local_numel)
+                    inner0 = getattr(shell, shell.__tensor_flatten__()[0][0])
+                    if inner0.dtype != local.dtype or inner0.numel() != pl.local_numel:
+                        raise AssertionError(
+                            f"all-gather extension {type(p.data).__name__}: the first inner tensor of new_zeros(n) must have n "
+                            f"elements of the parameter's dtype, got {inner0.numel()} x {inner0.dtype}")
+                    torch.utils.swap_tensors(inner0, self._master[pl.shard_offset : pl.shard_offset + pl.local_numel])
+                    sp.ext_local = shell
+                elif sp.ext_cls is not None:
                     sp.ext_local = local.as_subclass(sp.ext_cls)
                 for attr in ("_yf_init_fn",):
                     if hasattr(p, attr):
@@ -1046,19 +1059,57 @@ class ParamGroup:
             self.reshard()
 
     def reset_sharded_params(self) -> None:
-        """Re-derive the flat master after ``module._apply`` replaced the sharded parameters (``.to()``, ``.float()``)."""
-        new_dtype = None
+        """``module._apply`` (``.to()``, ``.float()``, ``.cuda()``) replaced the sharded parameters by transformed copies.
+
+        Before the first forward the flat master is re-derived from them, so the group really changes dtype / device.
+        After it, buffers, streams and views are bound to the master's storage: like the reference
+        (``ya_fsdp/_param.py:349-357``) the group then keeps its storage, takes over the transformed *values* (cast back to
+        the master's dtype) and registers its own sharded parameters again."""
+        def local_of(t: torch.Tensor) -> torch.Tensor:
+            return t._local_tensor if isinstance(t, RaggedShardDTensor) else t.data._local_tensor  # type: ignore[union-attr]
+
+        changed = False
         for sp in self.params:
             cur = sp.info.module._parameters[sp.info.param_name]
-            if cur is not sp.sharded_param and isinstance(cur, torch.Tensor):
-                new_dtype = cur.dtype
-        if new_dtype is None:
+            pl = sp.placement
+            assert pl is not None
+            if not isinstance(cur, torch.Tensor):
+                continue
+            # either a new Parameter object, or the same object whose data was swapped for the transformed tensor
+            if cur is not sp.sharded_param or (pl.local_numel and local_of(cur).data_ptr() != self._master[pl.shard_offset:].data_ptr()) \
+                    or cur.dtype != self._master.dtype:
+                changed = True
+        if not changed:
             return
         locals_ = []
         for sp in self.params:
             cur = sp.info.module._parameters[sp.info.param_name]
-            local = cur._local_tensor if isinstance(cur, RaggedShardDTensor) else cur.data._local_tensor  # type: ignore[union-attr]
-            locals_.append(local)
+            locals_.append(local_of(cur))
+        if self._lazy_inited:
+            with torch.no_grad():
+                for sp, local in zip(self.params, locals_):
+                    pl = sp.placement
+                    assert pl is not None and sp.sharded_param is not None
+                    mine = self._master[pl.shard_offset : pl.shard_offset + pl.local_numel]
+                    if pl.local_numel and (local.data_ptr() != mine.data_ptr() or local.dtype != mine.dtype):
+                        mine.copy_(local.reshape(-1))
+                    if local_of(sp.sharded_param) is not mine and (local_of(sp.sharded_param).dtype != mine.dtype
+                                                                   or local_of(sp.sharded_param).data_ptr() != mine.data_ptr()):
+                        # the registered Parameter object (the one optimizers hold) had its contents swapped for the transformed
+                        # tensor: swap the master-backed contents back in, so the object keeps its identity
+                        fresh = nn.Parameter(RaggedShardDTensor(mine, sp.sharded_param._spec.with_dtype(mine.dtype)),
+                                             requires_grad=sp.requires_grad)
+                        torch.utils.swap_tensors(sp.sharded_param, fresh)
+                    # gradients were transformed along with the parameters: drop them (the reference's re-created parameters
+                    # have none either) and bind fresh views of the flat sharded gradient
+                    sp.sharded_param.grad = None
+                    sp.to_sharded()
+                if self._sharded_grad_flat is not None:
+                    self._bind_sharded_grads()
+            self._ag_input_fresh = False  # the next gather re-derives the compute-dtype copy from the new values
+            self._secondary_valid = False
+            return
+        new_dtype = locals_[0].dtype
         device = locals_[0].device
         master = torch.zeros(self.layout.shard_numel, dtype=new_dtype, device=device)
         for sp, local in zip(self.params, locals_):
@@ -1079,8 +1130,6 @@ class ParamGroup:
             sp.sharded_param = nn.Parameter(RaggedShardDTensor(local, spec), requires_grad=sp.requires_grad)
             sp.sharded_grad = None
             sp.to_sharded()
-        if self._lazy_inited:
-            raise RuntimeError("changing dtype/device of a fully_shard module after its first forward is not supported")
 
     def _init_dtypes_after_apply(self) -> None:
         pd, rd = self.mp_policy.param_dtype, self.mp_policy.reduce_dtype

@@ -129,6 +129,14 @@ def main() -> None:
             kernels.gemm_scatter(dy, xx, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off, shard_numel=shard,
                                  rank=rank, world=world)
 
+    def dw_pushed_grouped(gbuf):
+        kernels.gemm_scatter_grouped([(dy, xx, off) for dy, xx, off in acts.values()], peer_grad=be._peers(gbuf), shard_numel=shard,
+                                     rank=rank, world=world)
+
+    grouped = os.environ.get("YF_GROUPED", "1") == "1"  # one rank-rotated launch for the layer (0: one launch per weight)
+    if grouped:
+        dw_pushed = dw_pushed_grouped  # noqa: F811
+
     def serial(fused: bool):
         def run():
             be.before_write(gbufs[0])
@@ -198,7 +206,7 @@ def main() -> None:
                         "fused_layer_buffer_equals_all_gather": same,
                         "roofline_ms": round(roof_ag, 4), "fused_fraction_of_roofline": round(roof_ag / t_fus, 3),
                         "best_unfused_fraction_of_roofline": round(roof_ag / best_unf, 3)},
-            "gemm_rs": {"dw_gemms_ms": round(t_dw, 4), "pushed_gemms_ms": round(t_scatter, 4),
+            "gemm_rs": {"grouped_rank_rotated_launch": grouped, "dw_gemms_ms": round(t_dw, 4), "pushed_gemms_ms": round(t_scatter, 4),
                         "pushed_gemms_fraction_of_roofline": round(roof_rs / t_scatter, 3),
                         "reduce_scatter_ms": {k: round(v, 4) for k, v in t_rs.items()},
                         "unfused_ms": {k: round(v, 4) for k, v in t_unf2.items()}, "fused_ms": round(t_fus2, 4),

@@ -160,8 +160,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     float m_run = -INFINITY, l_run = 0.f;    // l_run: this thread's half of the row sum
     const float sl2 = args.scale_log2;
     bool alive = true;
+    bool gave_up = false;  // this thread's bounded wait ran out: all 256 softmax threads leave together at the next barrier
     for (int j = 0; j < n_kv && alive; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, 120)) { alive = false; break; }
+      if (!gave_up && !mbar_wait(&s_full[j & 1], (j >> 1) & 1, 120)) gave_up = true;
       tc_fence_after();
       const uint32_t ts = tmem_S + lane_off + (j & 1) * 128;
       const int kv0 = j * BKV;
@@ -186,7 +187,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       // combine with the partner thread's half (buffers alternate with the block parity: one barrier per block)
       float* xm = xmax + (j & 1) * 256;
       xm[half * 128 + row] = mx;
-      named_bar_sync(2, 256);
+      if (named_bar_or(2, 256, gave_up)) { alive = false; break; }  // the barrier of the maximum exchange carries the give-up flag
       mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -223,7 +224,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
-      if (!mbar_wait(o_full, j & 1, 121)) { alive = false; break; }
+      if (!mbar_wait(o_full, j & 1, 121)) gave_up = true;  // taken by everybody at the next block's barrier (or below)
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -236,7 +237,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
     // total row sum = both halves
     xsum[half * 128 + row] = l_run;
-    named_bar_sync(2, 256);
+    if (named_bar_or(2, 256, gave_up)) alive = false;
     const float l_tot = l_run + xsum[(half ^ 1) * 128 + row];
     if (alive && q0 + row < args.S) {
       const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;

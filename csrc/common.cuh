@@ -145,6 +145,21 @@ YF_DEVINL void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int
 }
 YF_DEVINL void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 YF_DEVINL void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
+// named barrier that also ORs a predicate over its participants: every thread learns whether ANY of them raised it.  Used
+// where a bounded wait precedes a named barrier: a give-up must be taken by all participants together, otherwise the ones
+// that carried on would wait at the barrier for threads that have left.
+YF_DEVINL bool named_bar_or(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, %2, %3, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred), "r"(id), "r"(nthreads)
+      : "memory");
+  return out != 0;
+}
 YF_DEVINL void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 YF_DEVINL void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 YF_DEVINL void tma_store_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }

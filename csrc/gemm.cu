@@ -22,6 +22,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
+constexpr int MAX_RANKS = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int GATHER_THREADS = 224;  // gather mode: one more warp, for the communication role
 
@@ -47,15 +48,28 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
 };
 
+constexpr int MAX_GROUP = 4;  // problems of one grouped launch (the weight-gradient GEMMs of a decoder layer)
+
 struct GemmArgs {
   void* C;
   int M, N, K;
   long long ldc;
   float alpha;
   int a_mn, b_mn, out_f32, accumulate;
+  // Grouped launch (scatter mode): n_prob problems that share K and the operand majors, in the order of their positions in
+  // the flat layer gradient.  Tiles are numbered problem by problem, rows first; tile_prefix[p] = number of tiles in front
+  // of problem p; the launch walks the tiles starting at tile `rot` and wraps around.  n_prob == 0: one problem, M x N above.
+  int n_prob;
+  int Mp[MAX_GROUP], Np[MAX_GROUP];
+  long long flat_off[MAX_GROUP];
+  int tile_prefix[MAX_GROUP + 1];
+  int rot;
 };
 
-constexpr int MAX_RANKS = 16;
+// operand tensor maps of up to MAX_GROUP problems (entry 0 alone for an ordinary launch)
+struct GroupMaps {
+  CUtensorMap a[MAX_GROUP], b[MAX_GROUP];
+};
 
 // Arguments of the two fused compute + collective modes (both off when zero-initialised).
 //
@@ -190,8 +204,7 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long lo
 
 template <int BLOCK_N, int CG, int MODE>
 __global__ void __launch_bounds__(MODE == MODE_GATHER ? GATHER_THREADS : GEMM_THREADS, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
+gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant__ CUtensorMap tma_c, GemmArgs args, FusedArgs fa) {
   using Cfg = GemmCfg<BLOCK_N, CG, MODE>;
   // CG == 2: the grid is a sequence of CTA pairs (clusters of two); a pair works on one 256 x BLOCK_N tile, CTA `crank` of
   // the pair on its rows [crank * 128, +128) with the B rows [crank * BLOCK_N / 2, +BLOCK_N / 2) in its shared memory
@@ -216,16 +229,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int M = args.M, N = args.N, K = args.K;
-  const int num_m = (M + TILE_M - 1) / TILE_M;
-  const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int K = args.K;
+  const int num_m = (args.M + TILE_M - 1) / TILE_M;
+  const int num_n = (args.N + BLOCK_N - 1) / BLOCK_N;
   const int num_k = (K + BLOCK_K - 1) / BLOCK_K;
-  const int num_tiles = num_m * num_n;
+  const bool grouped = (MODE == MODE_SCATTER) && args.n_prob > 0;
+  const int num_tiles = grouped ? args.tile_prefix[args.n_prob] : num_m * num_n;
   constexpr int GROUP_M = 16 / CG;  // 2048 rows of A share a column block of B through L2
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tma_a);
-    tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&maps.a[0]);
+    tma_prefetch_desc(&maps.b[0]);
     tma_prefetch_desc(&tma_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -254,7 +268,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_coords = [&](int t, int& m0, int& n0) {
+  // tile t of this launch -> problem p, first row m0 (of this CTA) and first column n0 of the tile
+  auto tile_coords = [&](int t, int& p, int& m0, int& n0) {
+    if (grouped) {
+      int g = t + args.rot;
+      if (g >= num_tiles) g -= num_tiles;
+      p = 0;
+      while (p + 1 < args.n_prob && g >= args.tile_prefix[p + 1]) ++p;
+      const int local = g - args.tile_prefix[p];
+      const int nn = (args.Np[p] + BLOCK_N - 1) / BLOCK_N;
+      m0 = (local / nn) * TILE_M + (int)crank * BLOCK_M;
+      n0 = (local % nn) * BLOCK_N;
+      return;
+    }
+    p = 0;
     const int per_group = GROUP_M * num_n;
     const int g = t / per_group;
     const int first_m = g * GROUP_M;
@@ -270,8 +297,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t it = 0;
       bool alive = true;
       for (int t = unit; t < num_tiles && alive; t += nunits) {
-        int m0, n0;
-        tile_coords(t, m0, n0);
+        int p, m0, n0;
+        tile_coords(t, p, m0, n0);
+        const CUtensorMap* tma_a = &maps.a[p];
+        const CUtensorMap* tma_b = &maps.b[p];
+        const int N = grouped ? args.Np[p] : args.N;
         if (MODE == MODE_GATHER) {
           // the rows [n0, n0 + BLOCK_N) of B must have landed in the local layer buffer: the column block's counter says so
           const int blk = n0 / BLOCK_N;
@@ -303,30 +333,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             if (leader) mbar_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
             const uint32_t fb = mapa_shared(smem_u32(&full[s]), 0);
             if (!args.a_mn) {
-              tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
+              tma_load_2d_pair(sa, tma_a, fb, k0, m0);
             } else {
 #pragma unroll
-              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d_pair(sa + j * (BLOCK_K * 128), &tma_a, fb, m0 + j * 64, k0);
+              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d_pair(sa + j * (BLOCK_K * 128), tma_a, fb, m0 + j * 64, k0);
             }
             if (!args.b_mn) {
-              tma_load_2d_pair(sb, &tma_b, fb, k0, nb);
+              tma_load_2d_pair(sb, tma_b, fb, k0, nb);
             } else {
 #pragma unroll
-              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d_pair(sb + j * (BLOCK_K * 128), &tma_b, fb, nb + j * 64, k0);
+              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d_pair(sb + j * (BLOCK_K * 128), tma_b, fb, nb + j * 64, k0);
             }
           } else {
             mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
             if (!args.a_mn) {
-              tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+              tma_load_2d(sa, tma_a, &full[s], k0, m0);
             } else {
 #pragma unroll
-              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * (BLOCK_K * 128), &tma_a, &full[s], m0 + j * 64, k0);
+              for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * (BLOCK_K * 128), tma_a, &full[s], m0 + j * 64, k0);
             }
             if (!args.b_mn) {
-              tma_load_2d(sb, &tma_b, &full[s], k0, nb);
+              tma_load_2d(sb, tma_b, &full[s], k0, nb);
             } else {
 #pragma unroll
-              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d(sb + j * (BLOCK_K * 128), &tma_b, &full[s], nb + j * 64, k0);
+              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d(sb + j * (BLOCK_K * 128), tma_b, &full[s], nb + j * 64, k0);
             }
           }
         }
@@ -388,7 +418,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
   } else if (MODE == MODE_GATHER && warp == 6) {
     // ------------------------------------------------------------ communication role (gather mode)
-    if (lane == 0) gather_comm_role(fa, (long long)N * K * 2, (long long)BLOCK_N * K * 2, ring, ring_bars);
+    if (lane == 0) gather_comm_role(fa, (long long)args.N * K * 2, (long long)BLOCK_N * K * 2, ring, ring_bars);
   } else {
     // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
     // TMEM -> registers -> 128-byte-swizzled staging block in shared memory -> TMA store (or TMA
@@ -403,11 +433,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     uint32_t chunk_ctr = 0;
     float ss = 0.f;  // sum of squares of this thread's outputs (rows / columns past the edges are exact zeros)
     for (int t = unit; t < num_tiles && alive; t += nunits, ++lt) {
-      int m0, n0;
-      tile_coords(t, m0, n0);
+      int p, m0, n0;
+      tile_coords(t, p, m0, n0);
+      const int M = grouped ? args.Mp[p] : args.M, N = grouped ? args.Np[p] : args.N;
+      const long long c_flat_off = grouped ? args.flat_off[p] : fa.c_flat_off;
       const int acc = lt & 1;
       const uint32_t acc_ph = (lt >> 1) & 1;
-      if (!mbar_wait(&tfull[acc], acc_ph, 30)) { alive = false; break; }
+      const bool gave_up = !mbar_wait(&tfull[acc], acc_ph, 30);
+      if (MODE == MODE_SCATTER) {
+        if (!__all_sync(0xffffffffu, !gave_up)) { alive = false; break; }  // per-warp epilogue: a warp leaves as a whole
+      } else if (named_bar_or(1, 128, gave_up)) {  // the four warps share named barriers below: they leave together
+        alive = false;
+        break;
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
       const float alpha = args.alpha;
@@ -448,7 +486,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           const int col = n0 + c * SCATTER_COLS;
           if (m < M && col < N) {
             const long long ncols = min(SCATTER_COLS, N - col);
-            const long long f = fa.c_flat_off + (long long)m * N + col;   // position in the flat layer gradient
+            const long long f = c_flat_off + (long long)m * N + col;      // position in the flat layer gradient
             const long long o = f / fa.shard_numel;                       // owner rank
             const long long loc = f - o * fa.shard_numel;
             const long long first = min(ncols, fa.shard_numel - loc);
@@ -558,21 +596,64 @@ int ensure_smem_optin(KernelT kernel, int bytes, bool (&done)[64]) {
   return 0;
 }
 
+// One problem's operands (a grouped launch passes several).
+struct Operands {
+  const void* A;
+  const void* B;
+  long long lda, ldb;
+  int M, N;
+};
+
 template <int BLOCK_N, int CG, int MODE = MODE_PLAIN>
-int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
-                cudaStream_t stream) {
+int launch_gemm(const Operands* ops, int n_ops, GemmArgs args, const FusedArgs& fa, int sm_limit, cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N, CG, MODE>;
-  const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(A, args.M, args.K, lda, 64, BLOCK_K, 2, 1)
-                                    : yf_tensor_map_2d(A, args.K, args.M, lda, BLOCK_K, BLOCK_M, 2, 1);
-  const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(B, args.N, args.K, ldb, 64, BLOCK_K, 2, 1)
-                                    : yf_tensor_map_2d(B, args.K, args.N, ldb, BLOCK_K, Cfg::B_ROWS, 2, 1);
+  if (n_ops < 1 || n_ops > MAX_GROUP) return -1;
+  GroupMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int i = 0; i < n_ops; ++i) {
+    const Operands& o = ops[i];
+    const CUtensorMap* ma = args.a_mn ? yf_tensor_map_2d(o.A, o.M, args.K, o.lda, 64, BLOCK_K, 2, 1)
+                                      : yf_tensor_map_2d(o.A, args.K, o.M, o.lda, BLOCK_K, BLOCK_M, 2, 1);
+    const CUtensorMap* mb = args.b_mn ? yf_tensor_map_2d(o.B, o.N, args.K, o.ldb, 64, BLOCK_K, 2, 1)
+                                      : yf_tensor_map_2d(o.B, args.K, o.N, o.ldb, BLOCK_K, Cfg::B_ROWS, 2, 1);
+    if (!ma || !mb) return -2;
+    maps.a[i] = *ma;
+    maps.b[i] = *mb;
+  }
+  for (int i = n_ops; i < MAX_GROUP; ++i) {  // unused entries hold a valid descriptor all the same
+    maps.a[i] = maps.a[0];
+    maps.b[i] = maps.b[0];
+  }
   const CUtensorMap* mc = yf_tensor_map_2d(args.C, args.N, args.M, args.ldc, args.out_f32 ? 32 : 64, BLOCK_M, args.out_f32 ? 4 : 2, 1);
-  if (!ma || !mb || !mc) return -2;
+  if (!mc) return -2;
   static bool optin[64] = {};
   if (int rc = ensure_smem_optin(gemm_bf16_tcgen05_kernel<BLOCK_N, CG, MODE>, Cfg::SMEM_BYTES, optin)) return rc;
   if (int rc = yf_tu_bind_status()) return rc;
   const int tile_m = BLOCK_M * CG;
-  const int num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
+  int num_tiles = 0;
+  if (args.n_prob > 0) {
+    for (int i = 0; i < args.n_prob; ++i) {
+      args.tile_prefix[i] = num_tiles;
+      num_tiles += ((args.Mp[i] + tile_m - 1) / tile_m) * ((args.Np[i] + BLOCK_N - 1) / BLOCK_N);
+    }
+    args.tile_prefix[args.n_prob] = num_tiles;
+    // rank-rotated start: the first tile whose rows begin at or after the shard of the next rank, so that at any moment the
+    // ranks of the group push into different owners
+    args.rot = 0;
+    const long long target = (long long)((fa.rank + 1) % fa.world) * fa.shard_numel;
+    bool found = false;
+    for (int i = 0; i < args.n_prob && !found; ++i) {
+      const int nn = (args.Np[i] + BLOCK_N - 1) / BLOCK_N, nm = (args.Mp[i] + tile_m - 1) / tile_m;
+      for (int m = 0; m < nm; ++m)
+        if (args.flat_off[i] + (long long)m * tile_m * args.Np[i] >= target) {
+          args.rot = args.tile_prefix[i] + m * nn;
+          found = true;
+          break;
+        }
+    }
+  } else {
+    num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
+  }
   int sms = yf_num_sms();
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
   int units = sms / CG;
@@ -594,9 +675,16 @@ int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedA
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BLOCK_N, CG, MODE>, *ma, *mb, *mc, args, fa);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BLOCK_N, CG, MODE>, maps, *mc, args, fa);
   if (e != cudaSuccess) return -(int)e;
   return -(int)cudaGetLastError();
+}
+
+template <int BLOCK_N, int CG, int MODE = MODE_PLAIN>
+int launch_gemm(const void* A, const void* B, const GemmArgs& args, const FusedArgs& fa, long long lda, long long ldb, int sm_limit,
+                cudaStream_t stream) {
+  const Operands one = {A, B, lda, ldb, args.M, args.N};
+  return launch_gemm<BLOCK_N, CG, MODE>(&one, 1, args, fa, sm_limit, stream);
 }
 
 // Tile shape for a problem: CTA pairs (256 x 256 tiles, half of B per CTA) whenever both extents fill such a tile; single
@@ -651,6 +739,7 @@ extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, 
   if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
   GemmArgs args;
+  memset(&args, 0, sizeof(args));
   args.C = C;
   args.M = M; args.N = N; args.K = K;
   args.ldc = ldc;
@@ -686,6 +775,7 @@ extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K
        reinterpret_cast<uintptr_t>(layer_buf)) & 15)
     return -1;
   GemmArgs args;
+  memset(&args, 0, sizeof(args));
   args.C = C;
   args.M = M; args.N = N; args.K = K;
   args.ldc = ldc;
@@ -724,6 +814,7 @@ extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, 
   if (c_flat_off + (long long)M * N > shard_numel * world) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return -1;
   GemmArgs args;
+  memset(&args, 0, sizeof(args));
   args.C = peer_grad[rank];  // only used to build a (unused) store descriptor
   args.M = M; args.N = N; args.K = K;
   args.ldc = N;
@@ -744,4 +835,51 @@ extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, 
   fa.shard_numel = shard_numel;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return dispatch_gemm(A, B, args, fa, lda, ldb, sm_limit, s);
+}
+
+// The weight-gradient GEMMs of a whole layer as ONE launch, pushed to their owners (grouped GEMM -> reduce-scatter).
+// n problems (at most 4) dW_i[M_i, N_i] = A_i^T-or-not * B_i, sharing K and the operand majors, in the order of their
+// positions flat_off[i] in the flat layer gradient.  Every rank walks the same tile sequence (rows first) but starts at the
+// shard of the rank after it, so the ranks push into different owners at any moment and no owner's NVLink ingress becomes a
+// hot spot, which separate launches cannot avoid (all ranks would push the same rows at the same time).
+extern "C" int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const void* const* B, const int* M, const int* N, int K,
+                                            const long long* lda, const long long* ldb, int a_mn, int b_mn, float alpha,
+                                            void* const* peer_grad, const long long* flat_off, long long shard_numel, int rank,
+                                            int world, int sm_limit, void* stream) {
+  if (n < 1 || n > MAX_GROUP || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || (shard_numel % 4)) return -1;
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  Operands ops[MAX_GROUP];
+  bool all256 = true;
+  for (int i = 0; i < n; ++i) {
+    if (M[i] <= 0 || N[i] <= 0 || (lda[i] % 8) || (ldb[i] % 8) || (N[i] % 4) || (flat_off[i] % 4) || flat_off[i] < 0) return -1;
+    if (flat_off[i] + (long long)M[i] * N[i] > shard_numel * world) return -1;
+    if (i > 0 && flat_off[i] < flat_off[i - 1] + (long long)M[i - 1] * N[i - 1]) return -1;  // ascending, no overlap
+    if ((reinterpret_cast<uintptr_t>(A[i]) | reinterpret_cast<uintptr_t>(B[i])) & 15) return -1;
+    ops[i] = {A[i], B[i], lda[i], ldb[i], M[i], N[i]};
+    args.Mp[i] = M[i];
+    args.Np[i] = N[i];
+    args.flat_off[i] = flat_off[i];
+    all256 = all256 && M[i] >= 256 && N[i] >= 256;
+  }
+  args.n_prob = n;
+  args.C = peer_grad[rank];  // only used to build a (unused) store descriptor
+  args.M = M[0]; args.N = N[0]; args.K = K;
+  args.ldc = N[0];
+  args.alpha = alpha;
+  args.a_mn = a_mn ? 1 : 0;
+  args.b_mn = b_mn ? 1 : 0;
+  args.out_f32 = 1;
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  fa.scatter = 1;
+  fa.world = world; fa.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;
+    fa.peer_grad[r] = peer_grad[r];
+  }
+  fa.shard_numel = shard_numel;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (all256) return launch_gemm<256, 2, MODE_SCATTER>(ops, n, args, fa, sm_limit, s);
+  return launch_gemm<128, 1, MODE_SCATTER>(ops, n, args, fa, sm_limit, s);
 }

@@ -29,6 +29,12 @@ int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long
                          float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel, int rank, int world,
                          int sm_limit, void* stream);
 
+// grouped GEMM -> reduce-scatter: the weight-gradient GEMMs of a layer (n <= 4 problems sharing K and the operand majors, in
+// ascending order of flat_off) as one launch whose tile order is rotated by rank (see gemm.cu)
+int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const void* const* B, const int* M, const int* N, int K,
+                                 const long long* lda, const long long* ldb, int a_mn, int b_mn, float alpha, void* const* peer_grad,
+                                 const long long* flat_off, long long shard_numel, int rank, int world, int sm_limit, void* stream);
+
 // ---- memory-bound kernels (elementwise.cu)
 int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream);
 int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,

@@ -198,6 +198,33 @@ def _fused_worker(rank, world):
     torch.cuda.synchronize()
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-1), (got - want).abs().max().item()
     kernels.check_status()
+    # ---- the same as ONE grouped launch over three gradients of different shapes (tile order rotated by rank)
+    shapes = [(640, 384), (256, 384), (512, 768)]  # (rows, cols) of the three weights; the last has another input width
+    xs = {384: x, 768: torch.randn(t_tok, 768, device=dev).bfloat16()}
+    dys = [torch.randn(t_tok, r, device=dev).bfloat16() for r, _ in shapes]
+    offs, pos = [], 8 * 3
+    for r, c in shapes:
+        offs.append(pos)
+        pos += r * c + 8 * 11  # a gap after every matrix (norm weights sit between the matrices of a real layer)
+    gtotal = (pos + world * 8 - 1) // (world * 8) * (world * 8)
+    gshard = gtotal // world
+    gbuf2 = be.alloc(gtotal, torch.float32, dev, "reduce_input")
+    torch.cuda.synchronize()
+    be.barrier(3)
+    gbuf2.zero_()  # the gaps are not pushed by anybody in this test
+    be.barrier(3)
+    kernels.gemm_scatter_grouped([(dy_i, xs[c], off) for dy_i, (_, c), off in zip(dys, shapes, offs)], peer_grad=be._peers(gbuf2),
+                                 shard_numel=gshard, rank=rank, world=world)
+    got2 = torch.zeros(gshard, device=dev, dtype=torch.float32)
+    be.reduce_pushed(got2, gbuf2, scale=1.0 / world, accumulate=False)
+    local2 = torch.zeros(gtotal, device=dev, dtype=torch.float32)
+    for dy_i, (r, c), off in zip(dys, shapes, offs):
+        local2[off : off + r * c] = (dy_i.float().t() @ xs[c].float()).reshape(-1)
+    want2 = torch.empty(gshard, device=dev, dtype=torch.float32)
+    dist.reduce_scatter_tensor(want2, local2, op=dist.ReduceOp.AVG)
+    torch.cuda.synchronize()
+    assert torch.allclose(got2, want2, rtol=2e-2, atol=2e-1), (got2 - want2).abs().max().item()
+    kernels.check_status()
 
 
 def test_fused_gather_gemm_and_gemm_scatter():
@@ -271,3 +298,39 @@ def _train_fused_reduce_worker(rank, world):
 
 def test_training_with_fused_gemm_reduce_scatter():
     _run(_train_fused_reduce_worker, _world())
+
+
+def _hpz_worker(rank, world):
+    """Hierarchical partitioning on the peer-memory backend: the backward all-gather of the layers runs inside subgroups
+    of half the ranks, from secondary shards in peer-mapped memory; losses must match the plain configuration."""
+    import torch.distributed as dist
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.ops import kernels
+    from yafsdp_b200.optim import ShardedAdamW
+    from yafsdp_b200.train import TrainStep, build_llama
+
+    dev = torch.device("cuda", rank)
+    cfg = CONFIGS["tiny-gpu"]
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
+    n = max(1, world // 2)
+    groups = [dist.new_group(list(range(s, s + n))) for s in range(0, world, n)]
+    mine = groups[rank // n]
+    losses = {}
+    for hpz in (False, True):
+        model = build_llama(cfg, dev, comm_backend="symm")
+        if hpz:
+            for layer in model.model.layers:
+                layer.set_secondary_shard_group(mine)
+        opt = ShardedAdamW(model, lr=1e-3, max_grad_norm=1.0)
+        step = TrainStep(model, opt, dev)
+        losses[hpz] = [step(ids).item() for _ in range(3)]
+        kernels.check_status()
+        if hpz:
+            g = model.model.layers[0]._get_fsdp_state()._param_group
+            assert g._secondary_shard is not None and g._secondary_backend is model._get_fsdp_state()._comm_ctx.backend
+    for a, b in zip(losses[False], losses[True]):
+        assert abs(a - b) < 1e-3 * abs(a), losses
+
+
+def test_hierarchical_partitioning_on_peer_memory_backend():
+    _run(_hpz_worker, _world())

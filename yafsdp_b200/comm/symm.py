@@ -342,10 +342,40 @@ class SymmBackend(CommBackend):
         kernels._check(rc, "yf_reduce_scatter_pull")
         return sumsq is not None
 
+    def _subgroup(self, group: dist.ProcessGroup | None) -> list[int] | None:
+        """Arena indices of the ranks of ``group`` when it is a proper subgroup of the backend's group (hierarchical
+        partitioning gathers inside the ranks of one node), else ``None``."""
+        if group is None or group is self.group or group.size() == self.world:
+            return None
+        mine = dist.get_process_group_ranks(self.group)
+        return [mine.index(r) for r in dist.get_process_group_ranks(group)]
+
+    def subgroup_barrier(self) -> None:
+        """All ranks meet (on their current streams) before a gather inside subgroups reads shards that peers wrote during
+        the forward pass; the caller issues it once per backward pass."""
+        if not self.dry_run:
+            self.barrier(self.SLOT_SYNC)
+
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None) -> None:
         if self.dry_run:
             return
         nbytes = inp.numel() * inp.element_size()
+        sub = self._subgroup(group)
+        if sub is not None:
+            # inside a subgroup: copy engines or the pull kernel over the members' addresses (no multicast: the multicast
+            # object spans the whole group)
+            assert group is not None
+            peers = self._peer_ints(inp)
+            me, n = group.rank(), len(sub)
+            with torch.autograd._unsafe_preserve_version_counter(out):
+                if self.ag_transport == "sm":
+                    rc = _native.lib().yf_allgather_pull(_ptr_array([peers[i] for i in sub]), out.data_ptr(), nbytes, me, n, self.ag_ctas,
+                                                         torch.cuda.current_stream().cuda_stream)
+                    kernels._check(rc, "yf_allgather_pull")
+                else:
+                    base = out.data_ptr()
+                    self._ce_copies([(base + r * nbytes, peers[sub[r]], nbytes) for r in ((me + d) % n for d in range(n))], self._ag_ce_streams)
+            return
         mc_out = self.arena.mc_ptr(out) if self.ag_transport == "mc" else 0
         if mc_out:
             stream = torch.cuda.current_stream().cuda_stream

@@ -119,6 +119,7 @@ class CommContext:
         self.post_forward_order: list["ParamGroup"] = []
         self.backend: CommBackend = TorchBackend()
         self.groups: list["ParamGroup"] = []  # every group under the root, in module order (set at the root's lazy init)
+        self.secondary_synced = False  # hierarchical partitioning: the ranks have met since the secondary shards were written
 
     def lazy_init(self, device: torch.device, backend: CommBackend | None = None) -> None:
         self.streams = _DeviceStreams(device)
@@ -474,10 +475,19 @@ class ParamGroup:
         return self._data_flat[r * chunk : (r + 1) * chunk]
 
     def _save_secondary_shard(self) -> None:
+        assert self.comm_ctx is not None
+        self.comm_ctx.secondary_synced = False
         chunk = self._secondary_chunk()
         if self._secondary_shard is None:
-            self._secondary_shard = torch.empty_like(chunk)
-            self._secondary_backend = TorchBackend()
+            assert self.comm_ctx is not None
+            backend = self.comm_ctx.backend
+            if backend.needs_registered_buffers and hasattr(backend, "subgroup_barrier"):
+                # peer-memory backend: the secondary shards live in peer-mapped memory and are pulled over NVLink
+                self._secondary_shard = backend.alloc(chunk.numel(), chunk.dtype, self.device, "gather_input")
+                self._secondary_backend = backend
+            else:
+                self._secondary_shard = torch.empty_like(chunk)
+                self._secondary_backend = TorchBackend()
         self._secondary_shard.copy_(chunk)
         self._secondary_valid = True
 
@@ -687,6 +697,11 @@ class ParamGroup:
                         and (self._training_state != TrainingState.FORWARD or is_backward_running())):
                     # backward of a hierarchically partitioned group: the weights come from the secondary shards
                     assert self._secondary_shard is not None and self._secondary_backend is not None
+                    if self._secondary_backend.needs_registered_buffers and not cc.secondary_synced:
+                        # the peers wrote their secondary shards during their forward pass: meet once before the first pull
+                        st.wait_stream(stream, st.current())
+                        self._secondary_backend.subgroup_barrier()  # type: ignore[attr-defined]
+                        cc.secondary_synced = True
                     self._secondary_backend.all_gather(self._data_flat, self._secondary_shard, self.secondary_group)
                     self._gathered_from_secondary = True
                 else:

@@ -76,8 +76,10 @@ class _WeightGrad:
         self.sinks = [_sink(p) for p in params]
         self.use_sinks = all(s is not None for s in self.sinks)
 
-    def run(self, dy: torch.Tensor, x: torch.Tensor) -> list[torch.Tensor | None]:
-        """dW = dy^T x for the fused weight; returns per-parameter gradients (None when sunk)."""
+    def run(self, dy: torch.Tensor, x: torch.Tensor, deferred: "list[tuple[Any, ...]] | None" = None) -> list[torch.Tensor | None]:
+        """dW = dy^T x for the fused weight; returns per-parameter gradients (None when sunk).  ``deferred``: in push mode
+        the GEMM is not launched but recorded there, for one grouped launch at the end of the layer's backward
+        (:func:`flush_pushed`)."""
         if self.use_sinks and all(s.pushes() for s in self.sinks):
             # fused GEMM -> reduce-scatter: parameters that follow each other in the flat gradient are one GEMM
             i, r0 = 0, 0
@@ -88,8 +90,11 @@ class _WeightGrad:
                     _, off_j, *_ = self.sinks[j].begin_push()
                     assert off_j == nxt, "fused weights must be adjacent in the flat layout"
                     rows, nxt, j = rows + self.params[j].shape[0], nxt + self.params[j].numel(), j + 1
-                kernels.gemm_scatter(dy[:, r0 : r0 + rows], x, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off,
-                                     shard_numel=shard, rank=rank, world=world)
+                if deferred is not None:
+                    deferred.append((dy[:, r0 : r0 + rows], x, off, ptrs, shard, rank, world))
+                else:
+                    kernels.gemm_scatter(dy[:, r0 : r0 + rows], x, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off,
+                                         shard_numel=shard, rank=rank, world=world)
                 i, r0 = j, r0 + rows
             return [None] * len(self.params)
         if self.use_sinks:
@@ -111,6 +116,22 @@ class _WeightGrad:
             out.append(dw[r0 : r0 + p.shape[0]])
             r0 += p.shape[0]
         return out
+
+
+def flush_pushed(deferred: "list[tuple[Any, ...]]") -> None:
+    """Launch the recorded weight-gradient GEMMs of a layer: one grouped, rank-rotated launch when they share the token
+    dimension and the destination (the usual case), one launch each otherwise."""
+    if not deferred:
+        return
+    deferred.sort(key=lambda d: d[2])
+    _, _, _, ptrs, shard, rank, world = deferred[0]
+    same = all(d[3] is ptrs and d[0].shape[0] == deferred[0][0].shape[0] for d in deferred)
+    if same and len(deferred) <= 4:
+        kernels.gemm_scatter_grouped([(dy, x, off) for dy, x, off, *_ in deferred], peer_grad=ptrs, shard_numel=shard, rank=rank, world=world)
+    else:
+        for dy, x, off, p, sh, r, w in deferred:
+            kernels.gemm_scatter(dy, x, a_mn_major=True, b_mn_major=True, peer_grad=p, c_flat_off=off, shard_numel=sh, rank=r, world=w)
+    deferred.clear()
 
 
 def _norm_weight_grad(w: torch.Tensor, fn: Any) -> torch.Tensor | None:
@@ -203,28 +224,30 @@ class DecoderLayerFn(torch.autograd.Function):
         w_qkv = fuse_adjacent([wq, wk, wv])
         w_gu = fuse_adjacent([wg, wu])
         # ---- MLP
+        pushed: list[tuple[Any, ...]] = []  # push mode: the four weight-gradient GEMMs run as one grouped launch at the end
         da = kernels.gemm(dout, wd.detach(), b_mn_major=True)
-        (g_wd,) = _WeightGrad([wd]).run(dout, a)
+        (g_wd,) = _WeightGrad([wd]).run(dout, a, pushed)
         dgu = kernels.swiglu_bwd(gu, da)
         del da
         dn2 = kernels.gemm(dgu, w_gu, b_mn_major=True)
-        g_wg, g_wu = _WeightGrad([wg, wu]).run(dgu, n2)
+        g_wg, g_wu = _WeightGrad([wg, wu]).run(dgu, n2, pushed)
         del dgu
         box: list[torch.Tensor] = []
         g_n2 = _norm_weight_grad(w_n2, lambda dw: box.append(kernels.rmsnorm_bwd(h, w_n2.detach(), dn2, rstd2, dw, dres=dout)))
         dh = box.pop()
         # ---- attention
         datt = kernels.gemm(dh, wo.detach(), b_mn_major=True)
-        (g_wo,) = _WeightGrad([wo]).run(dh, att)
+        (g_wo,) = _WeightGrad([wo]).run(dh, att, pushed)
         dqkv = torch.empty_like(qkv)
         q, k, v = qkv[:, : hq * hd], qkv[:, hq * hd : (hq + hkv) * hd], qkv[:, (hq + hkv) * hd :]
         kernels.attn_bwd(q, k, v, att, datt, lse, dqkv[:, : hq * hd], dqkv[:, hq * hd : (hq + hkv) * hd],
                          dqkv[:, (hq + hkv) * hd :], dims.batch, dims.seq, hq, hkv, 1.0 / math.sqrt(hd), True)
         kernels.rope_(dqkv, cos_sin, dims.seq, 0, hq + hkv, hd, backward=True)
         dn1 = kernels.gemm(dqkv, w_qkv, b_mn_major=True)
-        g_wq, g_wk, g_wv = _WeightGrad([wq, wk, wv]).run(dqkv, n1)
+        g_wq, g_wk, g_wv = _WeightGrad([wq, wk, wv]).run(dqkv, n1, pushed)
         g_n1 = _norm_weight_grad(w_n1, lambda dw: box.append(kernels.rmsnorm_bwd(x, w_n1.detach(), dn1, rstd1, dw, dres=dh)))
         dx = box.pop()
+        flush_pushed(pushed)
         return dx, g_n1, g_wq, g_wk, g_wv, g_wo, g_n2, g_wg, g_wu, g_wd, None, None
 
 

@@ -145,6 +145,29 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool, b_mn_maj
     _check(rc, "yf_gemm_bf16_scatter")
 
 
+def gemm_scatter_grouped(problems: list[tuple[torch.Tensor, torch.Tensor, int]], *, peer_grad: Any, shard_numel: int, rank: int,
+                         world: int, alpha: float = 1.0, sm_limit: int = 0) -> None:
+    """The weight-gradient GEMMs of a layer as one launch pushed to their owners.  ``problems``: up to four
+    ``(dy [T, out], x [T, in], flat offset of the [out, in] gradient)`` in ascending flat order; every ``dW = dy^T x``
+    goes to the owners' slots for this rank.  The tile order is rotated by rank so that the ranks push into different
+    owners at any moment."""
+    n = len(problems)
+    assert 1 <= n <= 4
+    k = problems[0][0].shape[0]
+    a_ptrs = (ctypes.c_void_p * n)(*[dy.data_ptr() for dy, _, _ in problems])
+    b_ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for _, x, _ in problems])
+    ms = (ctypes.c_int * n)(*[dy.shape[1] for dy, _, _ in problems])
+    ns = (ctypes.c_int * n)(*[x.shape[1] for _, x, _ in problems])
+    ldas = (ctypes.c_longlong * n)(*[dy.stride(0) for dy, _, _ in problems])
+    ldbs = (ctypes.c_longlong * n)(*[x.stride(0) for _, x, _ in problems])
+    offs = (ctypes.c_longlong * n)(*[off for _, _, off in problems])
+    for dy, x, _ in problems:
+        assert dy.dtype == x.dtype == torch.bfloat16 and dy.shape[0] == x.shape[0] == k and dy.stride(1) == 1 and x.stride(1) == 1
+    rc = _native.lib().yf_gemm_bf16_scatter_grouped(n, a_ptrs, b_ptrs, ms, ns, k, ldas, ldbs, 1, 1, float(alpha), peer_grad, offs,
+                                                    shard_numel, rank, world, int(sm_limit), _stream())
+    _check(rc, "yf_gemm_bf16_scatter_grouped")
+
+
 def push_flat(src: torch.Tensor | None, numel: int, flat_off: int, peer_grad: Any, shard_numel: int, rank: int, world: int) -> None:
     """Push ``numel`` fp32 values (``src``, or zeros when ``None``) that start at position ``flat_off`` of the flat layer
     gradient into the owners' reduce-scatter slots for this rank."""

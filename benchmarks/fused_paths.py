@@ -133,7 +133,7 @@ def main() -> None:
         kernels.gemm_scatter_grouped([(dy, xx, off) for dy, xx, off in acts.values()], peer_grad=be._peers(gbuf), shard_numel=shard,
                                      rank=rank, world=world)
 
-    grouped = os.environ.get("YF_GROUPED", "1") == "1"  # one rank-rotated launch for the layer (0: one launch per weight)
+    grouped = os.environ.get("YF_GROUPED", "1") == "1"  # one grouped launch for the layer (0: one launch per weight)
     if grouped:
         dw_pushed = dw_pushed_grouped  # noqa: F811
 
@@ -195,6 +195,17 @@ def main() -> None:
     t_scatter = timed(lambda: dw_pushed(gbufs[0]), dev)
     flops2 = 2.0 * t * (4 * d * d + 3 * f * d)
     roof_rs = max(flops2 / (peak * 1e9), (world - 1) * shard * 4 / (NVLINK_GBS * 1e6))
+    # the same fused path with the gradients on the wire as bf16 (reduce_dtype=bfloat16; the owner sums in fp32)
+    hbufs = [be.alloc(total, torch.bfloat16, dev, "reduce_input") for _ in range(2)]
+
+    def fused_bf16(gbuf):
+        be.before_write(gbuf)
+        kernels.gemm_scatter_grouped([(dy, xx, off) for dy, xx, off in acts.values()], peer_grad=be._peers(gbuf), shard_numel=shard,
+                                     rank=rank, world=world, wire_bf16=True)
+        be.reduce_pushed(dst, gbuf, scale=1.0 / world, accumulate=False)
+
+    t_fus_bf16 = timed(lambda: fused_bf16(hbufs[0]), dev)
+    roof_rs_bf16 = max(flops2 / (peak * 1e9), (world - 1) * shard * 2 / (NVLINK_GBS * 1e6))
     code, site = kernels.status()
     if rank == 0:
         best_unf = min(t_unf.values())
@@ -206,7 +217,7 @@ def main() -> None:
                         "fused_layer_buffer_equals_all_gather": same,
                         "roofline_ms": round(roof_ag, 4), "fused_fraction_of_roofline": round(roof_ag / t_fus, 3),
                         "best_unfused_fraction_of_roofline": round(roof_ag / best_unf, 3)},
-            "gemm_rs": {"grouped_rank_rotated_launch": grouped, "dw_gemms_ms": round(t_dw, 4), "pushed_gemms_ms": round(t_scatter, 4),
+            "gemm_rs": {"grouped_launch": grouped, "dw_gemms_ms": round(t_dw, 4), "pushed_gemms_ms": round(t_scatter, 4),
                         "pushed_gemms_fraction_of_roofline": round(roof_rs / t_scatter, 3),
                         "reduce_scatter_ms": {k: round(v, 4) for k, v in t_rs.items()},
                         "unfused_ms": {k: round(v, 4) for k, v in t_unf2.items()}, "fused_ms": round(t_fus2, 4),
@@ -214,7 +225,9 @@ def main() -> None:
                         "pipelined_per_layer_fused_ms": round(t_pipe_fus, 4),
                         "roofline_ms": round(roof_rs, 4), "fused_fraction_of_roofline": round(roof_rs / t_fus2, 3),
                         "pipelined_fused_fraction_of_roofline": round(roof_rs / t_pipe_fus, 3),
-                        "best_unfused_fraction_of_roofline": round(roof_rs / best_unf2, 3)},
+                        "best_unfused_fraction_of_roofline": round(roof_rs / best_unf2, 3),
+                        "bf16_wire": {"fused_ms": round(t_fus_bf16, 4), "roofline_ms": round(roof_rs_bf16, 4),
+                                      "fused_fraction_of_roofline": round(roof_rs_bf16 / t_fus_bf16, 3)}},
         }))
     dist.destroy_process_group()
 

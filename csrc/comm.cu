@@ -236,21 +236,30 @@ __global__ void __launch_bounds__(256) allgather_mc_kernel(const uint4* __restri
 // Push a contiguous range of the flat layer gradient (fp32, `numel` elements starting at flat position `flat_off`) into the
 // reduce-scatter slots of the ranks that own it: element f goes to peer_grad[f / shard] + rank * shard + f % shard.  A null
 // source pushes zeros.  For the small gradients (norm weights, biases) that no GEMM epilogue produces.
+template <bool BF16_WIRE>
 __global__ void __launch_bounds__(256) push_flat_kernel(const float4* __restrict__ src, long long nvec, long long flat_off, PeerPtrs peer_grad,
                                                         long long shard_numel, int rank) {
+  constexpr int EPV = BF16_WIRE ? 8 : 4;  // elements per 16-byte piece on the wire
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    const float4 v = src != nullptr ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    const long long f = flat_off + i * 4;
+    const long long f = flat_off + i * EPV;
     const long long o = f / shard_numel;
     const long long loc = f - o * shard_numel;
 #ifdef YF_DEBUG_BOUNDS
-    if (o < 0 || o >= MAX_RANKS || peer_grad.p[o] == nullptr || loc + 4 > shard_numel) {  // debug build: record and skip
+    if (o < 0 || o >= MAX_RANKS || peer_grad.p[o] == nullptr || loc + EPV > shard_numel) {  // debug build: record and skip
       yf_raise(YF_ERR_BAD_ARGUMENT, 41);
       continue;
     }
 #endif
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(peer_grad.p[o]) + (long long)rank * shard_numel + loc) = v;
+    if (BF16_WIRE) {
+      const float4 a = src != nullptr ? src[2 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 b = src != nullptr ? src[2 * i + 1] : make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint4 v = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_grad.p[o]) + (long long)rank * shard_numel + loc) = v;
+    } else {
+      const float4 v = src != nullptr ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(peer_grad.p[o]) + (long long)rank * shard_numel + loc) = v;
+    }
   }
 }
 
@@ -379,17 +388,23 @@ extern "C" int yf_allgather_mc(const void* in, void* mc_out, long long shard_byt
 }
 
 extern "C" int yf_push_flat(const float* src, long long numel, long long flat_off, void* const* peer_grad, long long shard_numel, int rank,
-                            int world, void* stream) {
+                            int world, int wire_bf16, void* stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || numel <= 0) return -1;
-  if ((numel % 4) || (flat_off % 4) || (shard_numel % 4) || flat_off < 0 || flat_off + numel > shard_numel * world) return -1;
+  const int epv = wire_bf16 ? 8 : 4;
+  if ((numel % epv) || (flat_off % epv) || (shard_numel % epv) || flat_off < 0 || flat_off + numel > shard_numel * world) return -1;
   if (reinterpret_cast<uintptr_t>(src) & 15) return -1;
   for (int r = 0; r < world; ++r)
     if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;
-  const long long nvec = numel / 4;
+  const long long nvec = numel / epv;
   long long blocks = (nvec + 255) / 256;
   if (blocks > 2 * yf_num_sms()) blocks = 2 * yf_num_sms();
-  push_flat_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4*>(src), nvec, flat_off,
-                                                                                   to_peers(peer_grad, world), shard_numel, rank);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (wire_bf16)
+    push_flat_kernel<true><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float4*>(src), nvec, flat_off, to_peers(peer_grad, world),
+                                                       shard_numel, rank);
+  else
+    push_flat_kernel<false><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float4*>(src), nvec, flat_off, to_peers(peer_grad, world),
+                                                        shard_numel, rank);
   return -(int)cudaGetLastError();
 }
 

@@ -22,7 +22,6 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int MAX_RANKS = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int GATHER_THREADS = 224;  // gather mode: one more warp, for the communication role
 
@@ -38,9 +37,9 @@ struct GemmCfg {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   static constexpr int B_BYTES = B_ROWS * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int RING_BYTES = (MODE == MODE_GATHER) ? 4 * 16384 : 0;  // the communication role's ring (COMM_SLOTS pieces)
+  static constexpr int RING_BYTES = (MODE == MODE_GATHER) ? 6 * 16384 : 0;  // the communication role's ring (COMM_SLOTS pieces)
   static constexpr int STAGES = (MODE == MODE_SCATTER) ? (STAGE_BYTES == 49152 ? 3 : 4)
-                                : (MODE == MODE_GATHER) ? (STAGE_BYTES == 49152 ? 2 : (STAGE_BYTES == 32768 ? 4 : 5))
+                                : (MODE == MODE_GATHER) ? (STAGE_BYTES == 49152 ? 2 : 3)
                                                         : ((STAGE_BYTES == 49152) ? 4 : 6);
   static constexpr int TMEM_COLS = 2 * BLOCK_N;  // two accumulators (power of two: 256 or 512)
   // plain: two [128 rows x 128 B] swizzled blocks for TMA stores; scatter: two [128 rows x 256 B (+ padding)] linear blocks
@@ -48,6 +47,7 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + 256;
 };
 
+constexpr int MAX_RANKS = 16;
 constexpr int MAX_GROUP = 4;  // problems of one grouped launch (the weight-gradient GEMMs of a decoder layer)
 
 struct GemmArgs {
@@ -57,13 +57,17 @@ struct GemmArgs {
   float alpha;
   int a_mn, b_mn, out_f32, accumulate;
   // Grouped launch (scatter mode): n_prob problems that share K and the operand majors, in the order of their positions in
-  // the flat layer gradient.  Tiles are numbered problem by problem, rows first; tile_prefix[p] = number of tiles in front
-  // of problem p; the launch walks the tiles starting at tile `rot` and wraps around.  n_prob == 0: one problem, M x N above.
+  // the flat layer gradient.  Tiles are numbered problem by problem, rows first (= in flat order); tile_prefix[p] = number
+  // of tiles in front of problem p; own_start[o] = first tile whose rows begin in the shard of rank o.  The launch deals the
+  // owners' tiles round-robin, starting with the rank after this one: step t works on tile t / world of owner
+  // (rank + 1 + t % world) % world, so every rank pushes to all owners (and computes for itself) all the time and no
+  // owner's NVLink ingress becomes a hot spot whatever the skew between the ranks.  n_prob == 0: one problem, M x N above.
   int n_prob;
   int Mp[MAX_GROUP], Np[MAX_GROUP];
   long long flat_off[MAX_GROUP];
   int tile_prefix[MAX_GROUP + 1];
-  int rot;
+  int own_start[MAX_RANKS + 1];
+  int steps;   // world * (largest number of tiles of one owner)
 };
 
 // operand tensor maps of up to MAX_GROUP problems (entry 0 alone for an ordinary launch)
@@ -98,6 +102,7 @@ struct FusedArgs {
   float* sumsq;
   // scatter
   int scatter;
+  int wire_bf16;                     // the slots hold bf16 (the owner accumulates in fp32); else fp32
   void* peer_grad[MAX_RANKS];
   long long c_flat_off, shard_numel;
 };
@@ -107,8 +112,8 @@ YF_DEVINL unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-YF_DEVINL void red_add_release_gpu_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+YF_DEVINL void red_add_relaxed_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 YF_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
@@ -127,9 +132,10 @@ YF_DEVINL void tma_store_wait1() { asm volatile("cp.async.bulk.wait_group 1;" ::
 // Communication role of the gather mode: ONE thread of every CTA.  Piece q of the layer (q = 0, 1, ...) is piece q / world
 // of the shard of rank (rank + q % world) % world, so consecutive pieces come from different owners and, at any moment, the
 // ranks read from different peers; CTA c moves the pieces c, c + grid, c + 2 grid, ...  A piece goes peer -> ring slot
-// (bulk load, completion on an mbarrier) -> local layer buffer (bulk store); two loads and two stores are in flight.
+// (bulk load, completion on an mbarrier) -> local layer buffer (bulk store); four loads and two stores are in flight.
 constexpr int COMM_PIECE = 16384;
-constexpr int COMM_SLOTS = 4;
+constexpr int COMM_SLOTS = 6;
+constexpr int COMM_AHEAD = 4;   // loads in flight per CTA (64 KB; x 148 CTAs covers the NVLink bandwidth-delay product with margin)
 
 __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long long block_bytes, uint8_t* ring, uint64_t* ring_bars) {
   const long long pps = (fa.shard_bytes + COMM_PIECE - 1) / COMM_PIECE;  // pieces per shard
@@ -157,18 +163,18 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long lo
     piece(i, src, off, bytes);
     long long lo = max(off, fa.b_byte_off) - fa.b_byte_off, hi = min(off + (long long)bytes, fa.b_byte_off + b_bytes) - fa.b_byte_off;
     if (lo >= hi) return;
-    // The piece's bulk store has completed (wait_group), so its bytes are in global memory; the release below orders them
-    // before the counter.  No proxy fence here: it would wait for every asynchronous operation this CTA has in flight (the
-    // GEMM's own loads and MMAs included) once per piece; the reader fences once per tile instead.
+    // The piece's bulk store has completed (wait_group): its bytes have been written at the L2, the point where the
+    // counter's atomic add is performed too, so the add cannot be seen before them.  No fence here: a release fence or a
+    // proxy fence waits for everything this SM has in flight (the GEMM's own loads, stores and MMAs), tens of microseconds
+    // per piece while the GEMM runs; the reader acquires and fences once per tile instead.
     while (lo < hi) {
       const long long blk = lo / block_bytes;
       const long long end = min(hi, (blk + 1) * block_bytes);
-      red_add_release_gpu_u64(fa.counters + blk, (unsigned long long)(end - lo));
+      red_add_relaxed_gpu_u64(fa.counters + blk, (unsigned long long)(end - lo));
       lo = end;
     }
   };
-  if (mine > 0) issue_load(0);
-  if (mine > 1) issue_load(1);
+  for (long long i = 0; i < COMM_AHEAD && i < mine; ++i) issue_load(i);
   long long done = 0, stored = 0;  // pieces published / pieces whose store has been issued
 #ifdef YF_GATHER_PROFILE
   unsigned long long tp[5] = {0, 0, 0, 0, 0};
@@ -187,7 +193,7 @@ __device__ void gather_comm_role(const FusedArgs& fa, long long b_bytes, long lo
     tma_store_commit();
     tma_store_wait_read1();  // every store but this one has finished reading its slot: the slot of piece i - 2 is free
     YF_TICK(1)
-    if (i + 2 < mine) issue_load(i + 2);
+    if (i + COMM_AHEAD < mine) issue_load(i + COMM_AHEAD);  // into slot (i + 4) % 6 == (i - 2) % 6
     YF_TICK(2)
     tma_store_wait1();       // every store but this one has completed: piece i - 1 is in the layer buffer
     YF_TICK(3)
@@ -234,7 +240,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
   const int num_n = (args.N + BLOCK_N - 1) / BLOCK_N;
   const int num_k = (K + BLOCK_K - 1) / BLOCK_K;
   const bool grouped = (MODE == MODE_SCATTER) && args.n_prob > 0;
-  const int num_tiles = grouped ? args.tile_prefix[args.n_prob] : num_m * num_n;
+  const int num_tiles = grouped ? args.steps : num_m * num_n;  // steps of the tile loop (a grouped step may be empty)
   constexpr int GROUP_M = 16 / CG;  // 2048 rows of A share a column block of B through L2
 
   if (threadIdx.x == 0) {
@@ -268,18 +274,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile t of this launch -> problem p, first row m0 (of this CTA) and first column n0 of the tile
-  auto tile_coords = [&](int t, int& p, int& m0, int& n0) {
+  // step t of this launch -> problem p, first row m0 (of this CTA) and first column n0 of the tile; false: empty step
+  auto tile_coords = [&](int t, int& p, int& m0, int& n0) -> bool {
     if (grouped) {
-      int g = t + args.rot;
-      if (g >= num_tiles) g -= num_tiles;
+      const int o = (fa.rank + 1 + t % fa.world) % fa.world;
+      const int g = args.own_start[o] + t / fa.world;
+      if (g >= args.own_start[o + 1]) return false;  // this owner has fewer tiles than the largest one
       p = 0;
       while (p + 1 < args.n_prob && g >= args.tile_prefix[p + 1]) ++p;
       const int local = g - args.tile_prefix[p];
       const int nn = (args.Np[p] + BLOCK_N - 1) / BLOCK_N;
       m0 = (local / nn) * TILE_M + (int)crank * BLOCK_M;
       n0 = (local % nn) * BLOCK_N;
-      return;
+      return true;
     }
     p = 0;
     const int per_group = GROUP_M * num_n;
@@ -289,6 +296,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
     const int r = t - g * per_group;
     m0 = (first_m + r % gsize) * TILE_M + (int)crank * BLOCK_M;
     n0 = (r / gsize) * BLOCK_N;
+    return true;
   };
 
   if (warp == 0) {
@@ -298,7 +306,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
       bool alive = true;
       for (int t = unit; t < num_tiles && alive; t += nunits) {
         int p, m0, n0;
-        tile_coords(t, p, m0, n0);
+        if (!tile_coords(t, p, m0, n0)) continue;
         const CUtensorMap* tma_a = &maps.a[p];
         const CUtensorMap* tma_b = &maps.b[p];
         const int N = grouped ? args.Np[p] : args.N;
@@ -376,9 +384,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
       uint32_t it = 0;
       bool alive = true;
       int lt = 0;
-      for (int t = unit; t < num_tiles && alive; t += nunits, ++lt) {
+      for (int t = unit; t < num_tiles && alive; t += nunits) {
+        {
+          int p, m0, n0;
+          if (!tile_coords(t, p, m0, n0)) continue;
+        }
         const int acc = lt & 1;
         const uint32_t acc_ph = (lt >> 1) & 1;
+        ++lt;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, 20)) { alive = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
@@ -432,13 +445,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
     int lt = 0;
     uint32_t chunk_ctr = 0;
     float ss = 0.f;  // sum of squares of this thread's outputs (rows / columns past the edges are exact zeros)
-    for (int t = unit; t < num_tiles && alive; t += nunits, ++lt) {
+    for (int t = unit; t < num_tiles && alive; t += nunits) {
       int p, m0, n0;
-      tile_coords(t, p, m0, n0);
+      if (!tile_coords(t, p, m0, n0)) continue;
       const int M = grouped ? args.Mp[p] : args.M, N = grouped ? args.Np[p] : args.N;
       const long long c_flat_off = grouped ? args.flat_off[p] : fa.c_flat_off;
       const int acc = lt & 1;
       const uint32_t acc_ph = (lt >> 1) & 1;
+      ++lt;
       const bool gave_up = !mbar_wait(&tfull[acc], acc_ph, 30);
       if (MODE == MODE_SCATTER) {
         if (!__all_sync(0xffffffffu, !gave_up)) { alive = false; break; }  // per-warp epilogue: a warp leaves as a whole
@@ -454,27 +468,50 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
         // TMEM lane into its own row of a staging block and sends that 256-byte piece with one bulk store (two where the
         // piece straddles a shard boundary) to the slot that the owning rank keeps for this rank.  No thread touches
         // another thread's row, so the epilogue needs no block-level barrier; bulk groups are per thread.
+        // Wire format fp32 (64 columns per piece) or bf16 (128 columns per piece; the owner still accumulates in fp32).
         const int m = m0 + r_in_tile;
+        const int esz = fa.wire_bf16 ? 2 : 4;
+        const int piece_cols = fa.wire_bf16 ? 2 * SCATTER_COLS : SCATTER_COLS;
+        const int n_pieces = BLOCK_N / piece_cols;
+        const long long align_mask = fa.wire_bf16 ? 7 : 3;  // 16-byte pieces
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N / SCATTER_COLS; ++c, ++chunk_ctr) {
+        for (int c = 0; c < n_pieces; ++c, ++chunk_ctr) {
           uint8_t* srow = staging + (chunk_ctr & 1) * (BLOCK_M * SCATTER_PITCH) + r_in_tile * SCATTER_PITCH;
           tma_store_wait_read1();  // the store that read this row two pieces ago has finished reading
+          if (fa.wire_bf16) {
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t r[32];
-            tmem_ld32(taddr + c * SCATTER_COLS + half * 32, r);
-            tmem_ld_wait();
+            for (int quarter = 0; quarter < 4; ++quarter) {
+              uint32_t r[32];
+              tmem_ld32(taddr + c * piece_cols + quarter * 32, r);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o;
-              o.x = alpha * __uint_as_float(r[4 * j + 0]);
-              o.y = alpha * __uint_as_float(r[4 * j + 1]);
-              o.z = alpha * __uint_as_float(r[4 * j + 2]);
-              o.w = alpha * __uint_as_float(r[4 * j + 3]);
-              *reinterpret_cast<float4*>(srow + half * 128 + j * 16) = o;
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 0]), alpha * __uint_as_float(r[8 * j + 1]));
+                o.y = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 2]), alpha * __uint_as_float(r[8 * j + 3]));
+                o.z = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 4]), alpha * __uint_as_float(r[8 * j + 5]));
+                o.w = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 6]), alpha * __uint_as_float(r[8 * j + 7]));
+                *reinterpret_cast<uint4*>(srow + quarter * 64 + j * 16) = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld32(taddr + c * piece_cols + half * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 o;
+                o.x = alpha * __uint_as_float(r[4 * j + 0]);
+                o.y = alpha * __uint_as_float(r[4 * j + 1]);
+                o.z = alpha * __uint_as_float(r[4 * j + 2]);
+                o.w = alpha * __uint_as_float(r[4 * j + 3]);
+                *reinterpret_cast<float4*>(srow + half * 128 + j * 16) = o;
+              }
             }
           }
-          if (c == BLOCK_N / SCATTER_COLS - 1) {  // accumulator fully read: hand it back to the MMA warp (of the leader CTA)
+          if (c == n_pieces - 1) {  // accumulator fully read: hand it back to the MMA warp (of the leader CTA)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -483,26 +520,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
             }
           }
           fence_proxy_async_smem();
-          const int col = n0 + c * SCATTER_COLS;
+          const int col = n0 + c * piece_cols;
           if (m < M && col < N) {
-            const long long ncols = min(SCATTER_COLS, N - col);
+            const long long ncols = min(piece_cols, N - col);
             const long long f = c_flat_off + (long long)m * N + col;      // position in the flat layer gradient
             const long long o = f / fa.shard_numel;                       // owner rank
             const long long loc = f - o * fa.shard_numel;
             const long long first = min(ncols, fa.shard_numel - loc);
 #ifdef YF_DEBUG_BOUNDS
             // debug build: a piece that would leave the owners' slots is recorded and skipped instead of stored
-            if (f < 0 || o >= fa.world || (first < ncols && o + 1 >= fa.world) || loc < 0 || (first & 3) || (loc & 3)) {
+            if (f < 0 || o >= fa.world || (first < ncols && o + 1 >= fa.world) || loc < 0 || (first & align_mask) || (loc & align_mask)) {
               yf_raise(YF_ERR_BAD_ARGUMENT, 40);
               tma_store_commit();
               continue;
             }
 #endif
-            float* dst = reinterpret_cast<float*>(fa.peer_grad[o]) + (long long)fa.rank * fa.shard_numel + loc;
-            bulk_store(dst, srow, (uint32_t)(first * 4));
+            (void)align_mask;
+            uint8_t* dst = reinterpret_cast<uint8_t*>(fa.peer_grad[o]) + ((long long)fa.rank * fa.shard_numel + loc) * esz;
+            bulk_store(dst, srow, (uint32_t)(first * esz));
             if (first < ncols) {
-              float* dst2 = reinterpret_cast<float*>(fa.peer_grad[o + 1]) + (long long)fa.rank * fa.shard_numel;
-              bulk_store(dst2, srow + first * 4, (uint32_t)((ncols - first) * 4));
+              uint8_t* dst2 = reinterpret_cast<uint8_t*>(fa.peer_grad[o + 1]) + (long long)fa.rank * fa.shard_numel * esz;
+              bulk_store(dst2, srow + first * esz, (uint32_t)((ncols - first) * esz));
             }
           }
           tma_store_commit();
@@ -637,20 +675,20 @@ int launch_gemm(const Operands* ops, int n_ops, GemmArgs args, const FusedArgs& 
       num_tiles += ((args.Mp[i] + tile_m - 1) / tile_m) * ((args.Np[i] + BLOCK_N - 1) / BLOCK_N);
     }
     args.tile_prefix[args.n_prob] = num_tiles;
-    // rank-rotated start: the first tile whose rows begin at or after the shard of the next rank, so that at any moment the
-    // ranks of the group push into different owners
-    args.rot = 0;
-    const long long target = (long long)((fa.rank + 1) % fa.world) * fa.shard_numel;
-    bool found = false;
-    for (int i = 0; i < args.n_prob && !found; ++i) {
+    // own_start[o]: first tile (in flat order) whose rows begin in the shard of rank o or later
+    int g = 0, o = 0, most = 0;
+    args.own_start[0] = 0;
+    for (int i = 0; i < args.n_prob; ++i) {
       const int nn = (args.Np[i] + BLOCK_N - 1) / BLOCK_N, nm = (args.Mp[i] + tile_m - 1) / tile_m;
-      for (int m = 0; m < nm; ++m)
-        if (args.flat_off[i] + (long long)m * tile_m * args.Np[i] >= target) {
-          args.rot = args.tile_prefix[i] + m * nn;
-          found = true;
-          break;
-        }
+      for (int m = 0; m < nm; ++m, g += nn) {
+        const long long owner = (args.flat_off[i] + (long long)m * tile_m * args.Np[i]) / fa.shard_numel;
+        while (o < owner && o < fa.world - 1) args.own_start[++o] = g;
+      }
     }
+    while (o < MAX_RANKS) args.own_start[++o] = num_tiles;
+    for (int r = 0; r < fa.world; ++r) most = most > args.own_start[r + 1] - args.own_start[r] ? most : args.own_start[r + 1] - args.own_start[r];
+    args.steps = most * fa.world;
+    num_tiles = args.steps;
   } else {
     num_tiles = ((args.M + tile_m - 1) / tile_m) * ((args.N + BLOCK_N - 1) / BLOCK_N);
   }
@@ -804,13 +842,15 @@ extern "C" int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K
 // GEMM -> reduce-scatter in one kernel.  dW[M,N] = A * B^T in fp32 is not stored locally: each 16-byte piece is
 // pushed into the staging slot `rank` of the rank that owns its position c_flat_off + m*N + n of the flat layer
 // gradient (peer_grad[o] = base of owner o's reduce buffer, laid out as `world` slots of shard_numel floats).
-// shard_numel must be a multiple of 4 and N a multiple of 4.  The owners sum their slots afterwards
+// wire_bf16: the slots hold bf16 instead of fp32 (half the NVLink bytes; the owner still sums in fp32).  shard_numel, N and
+// c_flat_off must be multiples of 4 (8 with the bf16 wire).  The owners sum their slots afterwards
 // (yf_reduce_scatter_pull on local slot pointers) once every rank's pushes are complete.
 extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int a_mn,
                                     int b_mn, float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel,
-                                    int rank, int world, int sm_limit, void* stream) {
+                                    int rank, int world, int wire_bf16, int sm_limit, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
-  if ((lda % 8) || (ldb % 8) || (N % 4) || (shard_numel % 4) || (c_flat_off % 4) || c_flat_off < 0) return -1;
+  const int al = wire_bf16 ? 8 : 4;  // elements per 16 bytes on the wire
+  if ((lda % 8) || (ldb % 8) || (N % al) || (shard_numel % al) || (c_flat_off % al) || c_flat_off < 0) return -1;
   if (c_flat_off + (long long)M * N > shard_numel * world) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return -1;
   GemmArgs args;
@@ -826,6 +866,7 @@ extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, 
   FusedArgs fa;
   memset(&fa, 0, sizeof(fa));
   fa.scatter = 1;
+  fa.wire_bf16 = wire_bf16 ? 1 : 0;
   fa.world = world; fa.rank = rank;
   for (int r = 0; r < world; ++r) {
     if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;
@@ -839,20 +880,21 @@ extern "C" int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, 
 
 // The weight-gradient GEMMs of a whole layer as ONE launch, pushed to their owners (grouped GEMM -> reduce-scatter).
 // n problems (at most 4) dW_i[M_i, N_i] = A_i^T-or-not * B_i, sharing K and the operand majors, in the order of their
-// positions flat_off[i] in the flat layer gradient.  Every rank walks the same tile sequence (rows first) but starts at the
-// shard of the rank after it, so the ranks push into different owners at any moment and no owner's NVLink ingress becomes a
-// hot spot, which separate launches cannot avoid (all ranks would push the same rows at the same time).
+// positions flat_off[i] in the flat layer gradient.  Every rank deals the owners' tiles round-robin (owner rank + 1 first), so
+// it pushes to all owners all the time and no owner's NVLink ingress becomes a hot spot, which separate launches cannot
+// avoid (all ranks would push the same rows, i.e. to the same one or two owners, at the same time).
 extern "C" int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const void* const* B, const int* M, const int* N, int K,
                                             const long long* lda, const long long* ldb, int a_mn, int b_mn, float alpha,
                                             void* const* peer_grad, const long long* flat_off, long long shard_numel, int rank,
-                                            int world, int sm_limit, void* stream) {
-  if (n < 1 || n > MAX_GROUP || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || (shard_numel % 4)) return -1;
+                                            int world, int wire_bf16, int sm_limit, void* stream) {
+  const int al = wire_bf16 ? 8 : 4;  // elements per 16 bytes on the wire
+  if (n < 1 || n > MAX_GROUP || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || (shard_numel % al)) return -1;
   GemmArgs args;
   memset(&args, 0, sizeof(args));
   Operands ops[MAX_GROUP];
   bool all256 = true;
   for (int i = 0; i < n; ++i) {
-    if (M[i] <= 0 || N[i] <= 0 || (lda[i] % 8) || (ldb[i] % 8) || (N[i] % 4) || (flat_off[i] % 4) || flat_off[i] < 0) return -1;
+    if (M[i] <= 0 || N[i] <= 0 || (lda[i] % 8) || (ldb[i] % 8) || (N[i] % al) || (flat_off[i] % al) || flat_off[i] < 0) return -1;
     if (flat_off[i] + (long long)M[i] * N[i] > shard_numel * world) return -1;
     if (i > 0 && flat_off[i] < flat_off[i - 1] + (long long)M[i - 1] * N[i - 1]) return -1;  // ascending, no overlap
     if ((reinterpret_cast<uintptr_t>(A[i]) | reinterpret_cast<uintptr_t>(B[i])) & 15) return -1;
@@ -873,6 +915,7 @@ extern "C" int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const v
   FusedArgs fa;
   memset(&fa, 0, sizeof(fa));
   fa.scatter = 1;
+  fa.wire_bf16 = wire_bf16 ? 1 : 0;
   fa.world = world; fa.rank = rank;
   for (int r = 0; r < world; ++r) {
     if (!peer_grad[r] || (reinterpret_cast<uintptr_t>(peer_grad[r]) & 15)) return -1;

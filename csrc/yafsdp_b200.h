@@ -27,13 +27,14 @@ int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long
                           void* counters, long long epoch, void* stream);
 int yf_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int a_mn, int b_mn,
                          float alpha, void* const* peer_grad, long long c_flat_off, long long shard_numel, int rank, int world,
-                         int sm_limit, void* stream);
+                         int wire_bf16, int sm_limit, void* stream);
 
 // grouped GEMM -> reduce-scatter: the weight-gradient GEMMs of a layer (n <= 4 problems sharing K and the operand majors, in
-// ascending order of flat_off) as one launch whose tile order is rotated by rank (see gemm.cu)
+// ascending order of flat_off) as one launch that deals the owners' tiles round-robin (see gemm.cu)
 int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const void* const* B, const int* M, const int* N, int K,
                                  const long long* lda, const long long* ldb, int a_mn, int b_mn, float alpha, void* const* peer_grad,
-                                 const long long* flat_off, long long shard_numel, int rank, int world, int sm_limit, void* stream);
+                                 const long long* flat_off, long long shard_numel, int rank, int world, int wire_bf16, int sm_limit,
+                                 void* stream);
 
 // ---- memory-bound kernels (elementwise.cu)
 int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream);
@@ -84,9 +85,10 @@ int yf_reduce_scatter_mc(const void* mc_in, float* dst, long long shard_numel, i
                          int bf16_wire, int n_ctas, float* sumsq, void* stream);
 int yf_allgather_mc(const void* in, void* mc_out, long long shard_bytes, int rank, int world, int n_ctas, void* stream);
 // Push fp32 values of the flat layer gradient into the owners' reduce-scatter slots (companion of yf_gemm_bf16_scatter for
-// gradients that no GEMM produces); src may be null (zeros).  numel, flat_off and shard_numel must be multiples of 4.
+// gradients that no GEMM produces); src may be null (zeros).  numel, flat_off and shard_numel must be multiples of 4 (8 with
+// the bf16 wire format, where the values are rounded to bf16 on the way).
 int yf_push_flat(const float* src, long long numel, long long flat_off, void* const* peer_grad, long long shard_numel, int rank,
-                 int world, void* stream);
+                 int world, int wire_bf16, void* stream);
 // Signal pads (sequence-numbered flags in every rank's peer-mapped pad): mode 1 = raise this rank's word of `slot` to `seq`
 // in every pad, mode 2 = wait (bounded) until every rank's word of `slot` in the own pad has reached `seq`, 3 = both.
 int yf_signal_pad(void* const* pads, int rank, int world, int slot, long long seq, long long timeout_ms, int mode, void* stream);

@@ -165,8 +165,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_attn_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_gemm_bf16_sumsq": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _F, _I, _P, _P],
         "yf_gemm_bf16_gathered": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _P, _L, _L, _I, _I, _P, _L, _P],
-        "yf_gemm_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _F, _P, _L, _L, _I, _I, _I, _P],
-        "yf_gemm_bf16_scatter_grouped": [_I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _P, _P, _L, _I, _I, _I, _P],
+        "yf_gemm_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _F, _P, _L, _L, _I, _I, _I, _I, _P],
+        "yf_gemm_bf16_scatter_grouped": [_I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _P, _P, _L, _I, _I, _I, _I, _P],
         "yf_allgather_pull": [_P, _P, _L, _I, _I, _I, _P],
         "yf_reduce_scatter_pull": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P],
         "yf_reduce_scatter_pull_sumsq": [_P, _P, _L, _I, _I, _F, _I, _I, _I, _P, _P],
@@ -174,7 +174,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_allgather_mc": [_P, _P, _L, _I, _I, _I, _P],
         "yf_signal_barrier": [_P, _I, _I, _I, _L, _L, _P],
         "yf_signal_pad": [_P, _I, _I, _I, _L, _L, _I, _P],
-        "yf_push_flat": [_P, _L, _L, _P, _L, _I, _I, _P],
+        "yf_push_flat": [_P, _L, _L, _P, _L, _I, _I, _I, _P],
         "yf_flag_wait": [_P, _L, _L, _L, _P],
         "yf_flag_set": [_P, _L, _L, _P],
         "yf_memcpy_async": [_P, _P, _L, _P],

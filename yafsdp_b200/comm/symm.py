@@ -397,6 +397,27 @@ class SymmBackend(CommBackend):
                                                  torch.cuda.current_stream().cuda_stream)
         kernels._check(rc, "yf_allgather_pull")
 
+    def gather_ranges(self, out: torch.Tensor, inp: torch.Tensor, ranges: list[tuple[int, int]]) -> None:
+        """Copy the element ranges ``[lo, hi)`` of the gathered tensor ``out`` from the shards that hold them (``inp`` is
+        this rank's shard; every rank's has the same size), on the current stream.  For the few small values that are
+        needed before a kernel that gathers the rest itself (:func:`yafsdp_b200.ops.kernels.gemm_gathered`)."""
+        if self.dry_run:
+            return
+        esz, shard = inp.element_size(), inp.numel()
+        peers = self._peer_ints(inp)
+        lib = _native.lib()
+        stream = torch.cuda.current_stream().cuda_stream
+        with torch.autograd._unsafe_preserve_version_counter(out):
+            for lo, hi in ranges:
+                while lo < hi:
+                    r = lo // shard
+                    end = min(hi, (r + 1) * shard)
+                    rc = lib.yf_memcpy_async(out.data_ptr() + lo * esz, peers[r] + (lo - r * shard) * esz, (end - lo) * esz, stream)
+                    if rc != 0:
+                        raise RuntimeError(f"peer copy failed with code {rc}")
+                    kernels._launches += 1
+                    lo = end
+
     def reduce_scatter(self, dst: torch.Tensor, inp: torch.Tensor, group: dist.ProcessGroup | None, *, scale: float,
                        accumulate: bool, acc_fp32: bool = True, sumsq: torch.Tensor | None = None) -> bool:
         if dst.dtype != torch.float32 or inp.dtype not in (torch.float32, torch.bfloat16):
@@ -454,8 +475,9 @@ class SymmBackend(CommBackend):
         one shard each) holds what every rank pushed for this rank's shard; wait until all pushes have landed, then
         ``dst (+)= scale * sum of the slots`` in rank order (fp32, deterministic), optionally with the squared norm.
         Positions of the flat gradient at or beyond ``valid_numel`` (the layout's padding) are zeroed first."""
-        if dst.dtype != torch.float32 or slots.dtype != torch.float32:
-            raise NotImplementedError("pushed gradients are fp32")
+        if dst.dtype != torch.float32 or slots.dtype not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError("pushed gradients travel as fp32 or bf16 and are summed into fp32")
+        esz = slots.element_size()
         shard = slots.numel() // self.world
         if self.dry_run:
             return self._reduce_own_chunk(dst, slots, shard, scale, accumulate, sumsq)
@@ -466,9 +488,9 @@ class SymmBackend(CommBackend):
             if lo < shard:
                 slots.view(self.world, shard)[:, lo:].zero_()  # nobody pushes the padding
         base = slots.data_ptr()
-        srcs = _ptr_array([base + (r - self.rank) * shard * 4 for r in range(self.world)])  # the kernel adds rank * shard
+        srcs = _ptr_array([base + (r - self.rank) * shard * esz for r in range(self.world)])  # the kernel adds rank * shard
         rc = _native.lib().yf_reduce_scatter_pull_sumsq(srcs, dst.data_ptr(), shard, self.rank, self.world, float(scale), int(accumulate),
-                                                        0, self.rs_ctas, None if sumsq is None else sumsq.data_ptr(),
+                                                        int(esz == 2), self.rs_ctas, None if sumsq is None else sumsq.data_ptr(),
                                                         torch.cuda.current_stream().cuda_stream)
         kernels._check(rc, "yf_reduce_scatter_pull")
         self._pad(self.SLOT_RS_DONE, seq, 1)  # peers may push into these slots again (before_write() waits for this)

@@ -326,6 +326,21 @@ class YaFSDPModule:
             if state._param_group is not None:
                 state._param_group.fused_reduce = enable
 
+    def set_fused_gather(self, enable: bool = True, prefix_params: Iterable[nn.Parameter] = ()) -> None:
+        """Fuse this module's all-gather into its first GEMM (peer-memory backend, bf16 gather): a forward pass whose gather
+        has not been started yet (nothing could prefetch it: the first layer of a step) skips the all-gather; the module's
+        forward redeems ``ParamGroup.take_in_kernel_gather`` and runs ``kernels.gemm_gathered``, which pulls the whole layer
+        from the peers while it computes (replaces ``ya_fsdp/_collectives.py:47-72`` + the GEMM).  ``prefix_params``: the
+        parameters read before that GEMM (copied ahead of it).  Only for modules whose forward does so (the Llama decoder
+        layer of this package)."""
+        g = self._get_fsdp_state()._param_group
+        if g is None:
+            return
+        wanted = {id(p) for p in prefix_params}
+        for grp in getattr(g, "groups", [g]):
+            grp.fused_gather = enable
+            grp.fused_gather_prefix = [sp.index for sp in grp.params if id(sp.sharded_param) in wanted or id(sp.unsharded_param) in wanted]
+
     def set_secondary_shard_group(self, group: Any, *, recurse: bool = False) -> None:
         """Hierarchical partitioning for this module's parameter group: gather the weights for backward inside ``group``
         (e.g. the ranks of one node) from a secondary shard saved after the forward all-gather."""

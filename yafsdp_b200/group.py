@@ -196,9 +196,15 @@ class GradSink:
         (``ParamGroup.fused_reduce``) instead of writing them into the local flat buffer."""
         return self.group._push_mode()
 
-    def begin_push(self) -> tuple[Any, int, int, int, int]:
+    @property
+    def local_ok(self) -> bool:
+        """Kernels may write this sink locally (fp32 view of the flat reduce buffer).  With a bf16 reduce dtype the sink
+        only exists for pushing: the pushed pieces are rounded to bf16 on the way and summed in fp32 by the owner."""
+        return self.view.dtype == torch.float32
+
+    def begin_push(self) -> tuple[Any, int, int, int, int, bool]:
         """Claim the reduce buffers for a pushed write of the whole parameter; returns what the pushing kernel needs:
-        ``(peer buffer pointers, flat offset of the parameter, shard size, rank, world)``."""
+        ``(peer buffer pointers, flat offset of the parameter, shard size, rank, world, bf16 wire format)``."""
         g = self.group
         g._acquire_grad_buffer()
         if g._sink_written[self.index]:
@@ -208,14 +214,16 @@ class GradSink:
         g._sink_counts[self.index] += 1
         g._sink_written[self.index] = True
         g._pushed = True
-        return g._push_ptrs, g.layout.flat_offsets[self.index], g.layout.shard_numel, g.rank, g.world_size
+        return (g._push_ptrs, g.layout.flat_offsets[self.index], g.layout.shard_numel, g.rank, g.world_size,
+                g.reduce_scatter_dtype == torch.bfloat16)
 
     def push_from(self, grad: torch.Tensor | None) -> None:
         """Push a complete fp32 gradient of this parameter (``None``: zeros) that some other kernel produced."""
         from .ops import kernels
 
-        ptrs, off, shard, rank, world = self.begin_push()
-        kernels.push_flat(None if grad is None else grad.reshape(-1), self.group.params[self.index].numel, off, ptrs, shard, rank, world)
+        ptrs, off, shard, rank, world, bf16 = self.begin_push()
+        kernels.push_flat(None if grad is None else grad.reshape(-1), self.group.params[self.index].numel, off, ptrs, shard, rank, world,
+                          wire_bf16=bf16)
 
     def begin(self, zero: bool = False) -> tuple[torch.Tensor, bool]:
         g = self.group
@@ -444,6 +452,15 @@ class ParamGroup:
         self.fused_reduce = False
         self._push_ptrs: Any = None
         self._pushed = False
+        # fused all-gather -> GEMM (peer-memory backend): a forward pass whose gather has not been started yet does not
+        # gather at all; the module's first GEMM (``kernels.gemm_gathered``) pulls the layer while it computes.  Only for
+        # modules whose forward asks for it (``take_in_kernel_gather``); ``fused_gather_prefix`` lists the parameters that
+        # are read before that GEMM and are therefore copied ahead of it (a norm weight).
+        self.fused_gather = False
+        self.fused_gather_prefix: list[int] = []
+        self._in_kernel_gather: dict[str, Any] | None = None
+        self._gather_counters: torch.Tensor | None = None
+        self._gather_epoch = 0
         # hierarchical partitioning: a secondary shard of the gathered weights kept inside a smaller (intra-node) group
         self.secondary_group: dist.ProcessGroup | None = None
         self._secondary_shard: torch.Tensor | None = None
@@ -594,16 +611,19 @@ class ParamGroup:
             # extension parameters get their unsharded tensor from fsdp_post_all_gather at the first unshard
             sp.unsharded_param = nn.Parameter(view, requires_grad=sp.requires_grad) if sp.ext_cls is None else None
             sp.rs_view = grad_flat[o : o + sp.numel].view(sp.orig_shape) if grad_flat is not None else None
-            # kernels write fp32 gradients into the sink; with a 16-bit reduce dtype the autograd .grad path is used instead
+            # kernels write fp32 gradients into the sink; with a bf16 reduce dtype the sink only serves pushed gradients
+            # (GradSink.local_ok) and the autograd .grad path is used otherwise
             sp.sink = (GradSink(self, sp.index, sp.rs_view)
-                       if sp.requires_grad and self.reduce_scatter_dtype == torch.float32 and sp.outer_mesh is None
-                       and sp.ext_cls is None else None)
+                       if sp.requires_grad and self.reduce_scatter_dtype in (torch.float32, torch.bfloat16) and sp.outer_mesh is None
+                       and sp.ext_cls is None and sp.rs_view is not None else None)
             if sp.unsharded_param is not None:
                 sp.unsharded_param._yf_grad_sink = sp.sink  # type: ignore[attr-defined]
+                sp.unsharded_param._yf_group_index = (self, sp.index)  # type: ignore[attr-defined]
         self._push_ptrs = None
+        al = 8 if self.reduce_scatter_dtype == torch.bfloat16 else 4  # elements per 16 bytes on the wire
         if (grad_flat is not None and not self._alias_grad and hasattr(backend, "reduce_pushed")
-                and self.reduce_scatter_dtype == torch.float32 and self.layout.shard_numel % 4 == 0
-                and all(sp.numel % 4 == 0 and sp.sink is not None for sp in self.params if sp.requires_grad)
+                and self.reduce_scatter_dtype in (torch.float32, torch.bfloat16) and self.layout.shard_numel % al == 0
+                and all(sp.numel % al == 0 and sp.sink is not None for sp in self.params if sp.requires_grad)
                 and all(sp.requires_grad for sp in self.params)):
             self._push_ptrs = backend.peer_pointers(grad_flat)  # type: ignore[attr-defined]
         self._register_state_dict_hooks()
@@ -764,11 +784,66 @@ class ParamGroup:
         logger.debug("pre_forward %s", self._module_fqn)
         with record_function(self._with_fqn("YaFSDP::pre_forward")):
             self._training_state = TrainingState.FORWARD
+            if self._can_gather_in_kernel():
+                self._begin_in_kernel_gather()
+                return
             self.unshard(self.unshard_async_op)
             self.wait_for_unshard()
 
+    # ------------------------------------------------------------------ fused all-gather -> GEMM
+    def _can_gather_in_kernel(self) -> bool:
+        if not self.fused_gather or self._is_unsharded or self._unshard_pending or self._alias_data or is_backward_running():
+            return False
+        cc = self.comm_ctx
+        return (cc is not None and hasattr(cc.backend, "gather_ranges") and not getattr(cc.backend, "dry_run", False)
+                and self.all_gather_dtype == torch.bfloat16 and not self._has_extensions and self.secondary_group is None
+                and self._ag_input_fresh and self._ag_input_version == self._master._version)
+
+    def _begin_in_kernel_gather(self) -> None:
+        """Forward pass without a gather: take the layer buffer, copy the few parameters that are read before the fusing
+        GEMM, register the (still empty) unsharded parameters and leave a ticket that the module's forward redeems with
+        :meth:`take_in_kernel_gather`."""
+        assert self.comm_ctx is not None and self.data_ctx is not None and self.comm_ctx.streams is not None
+        cc, st, ctx = self.comm_ctx, self.comm_ctx.streams, self.data_ctx
+        if ctx.owner is not None and ctx.owner is not self._owner:
+            raise RuntimeError(f"Data buffer {ctx.index} is still owned by {ctx.owner._module_fqn!r} while {self._module_fqn!r} needs it")
+        ctx.owner = self._owner
+        st.wait_event(None, ctx.release_event)
+        st.wait_stream(st.current(), cc.all_gather_stream)  # the step barrier (every rank's shards are final) sits there
+        backend = cc.backend
+        ranges = [(self.layout.flat_offsets[i], self.layout.flat_offsets[i] + self.params[i].numel) for i in self.fused_gather_prefix]
+        backend.gather_ranges(self._data_flat, self._ag_input, ranges)  # type: ignore[attr-defined]
+        if self._gather_counters is None:
+            self._gather_counters = torch.zeros(4096, dtype=torch.int64, device=self.device)
+        self._in_kernel_gather = {"peer_in": backend.peer_pointers(self._ag_input), "layer_buf": self._data_flat,  # type: ignore[attr-defined]
+                                  "shard_bytes": self.layout.shard_numel * 2, "rank": self.rank, "world": self.world_size,
+                                  "counters": self._gather_counters}
+        self._gathered_from_secondary = False
+        for sp in self.params:
+            sp.to_unsharded()
+        self._is_unsharded = True
+
+    def take_in_kernel_gather(self, first_param_index: int, rows: int) -> dict[str, Any] | None:
+        """Called by a module's forward right before its first GEMM over ``rows`` weight rows that start at parameter
+        ``first_param_index``: the arguments for ``kernels.gemm_gathered`` when this forward pass gathers in that kernel,
+        else ``None`` (the parameters are already there)."""
+        t = self._in_kernel_gather
+        if t is None:
+            return None
+        self._in_kernel_gather = None
+        if rows > 128 * t["counters"].numel():
+            raise RuntimeError("fused all-gather -> GEMM: more weight rows than column-block counters")
+        self._gather_epoch += 1
+        t["epoch"] = self._gather_epoch
+        t["b_byte_off"] = self.layout.flat_offsets[first_param_index] * 2
+        return t
+
     def post_forward(self) -> None:
         logger.debug("post_forward %s", self._module_fqn)
+        if self._in_kernel_gather is not None:
+            self._in_kernel_gather = None
+            raise RuntimeError(f"{self._module_fqn}: fused_gather is set but the module's forward never gathered its parameters "
+                               "(only modules that call take_in_kernel_gather may use it)")
         with record_function(self._with_fqn("YaFSDP::post_forward")):
             if not is_backward_running():  # inside backward (checkpoint recompute) the backward owns the buffer
                 if self.reshard_after_forward:

@@ -242,7 +242,7 @@ def _run_head(norm: RMSNorm, lm_head: LMHead, h: torch.Tensor, labels: torch.Ten
 def shard_llama(model: LlamaForCausalLM, *, mesh: Any = None, mp_policy: MixedPrecisionPolicy | None = None,
                 reshard_after_forward: bool | None = True, comm_backend: Any = None,
                 num_grad_buffers: int | None = 2, checkpoint_layers: int = 0, fused_reduce: bool | None = None,
-                **backend_options: Any) -> LlamaForCausalLM:
+                fused_gather: bool | None = None, **backend_options: Any) -> LlamaForCausalLM:
     """Wrap a Llama model: embedding, each decoder layer and ``[norm, lm_head]`` become groups, the model itself the
     parameter-less root.  ``checkpoint_layers`` wraps the first N layers' forward in activation checkpointing."""
     mp_policy = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
@@ -259,6 +259,13 @@ def shard_llama(model: LlamaForCausalLM, *, mesh: Any = None, mp_policy: MixedPr
         raise NotImplementedError("shard_llama: tied embeddings are not supported (wrap embed_tokens, norm and lm_head as one group yourself)")
     fully_shard([model.model.norm, model.lm_head], **kw)
     fully_shard(model, **kw)
+    if fused_gather is None:
+        fused_gather = os.environ.get("YAFSDP_FUSED_GATHER", "1") == "1"
+    if fused_gather and len(model.model.layers) > 0:
+        # the first layer's gather is the one nothing can hide (the step starts with it): its QKV GEMM pulls the layer itself;
+        # every later layer's gather is issued ahead of time on the communication stream
+        first = model.model.layers[0]
+        first.set_fused_gather(True, prefix_params=[first.input_layernorm.weight])  # type: ignore[attr-defined]
     if fused_reduce is None:
         fused_reduce = os.environ.get("YAFSDP_FUSED_REDUCE", "0") == "1"
     if fused_reduce:

@@ -84,20 +84,20 @@ class _WeightGrad:
             # fused GEMM -> reduce-scatter: parameters that follow each other in the flat gradient are one GEMM
             i, r0 = 0, 0
             while i < len(self.sinks):
-                ptrs, off, shard, rank, world = self.sinks[i].begin_push()
+                ptrs, off, shard, rank, world, bf16 = self.sinks[i].begin_push()
                 rows, nxt, j = self.params[i].shape[0], off + self.params[i].numel(), i + 1
                 while j < len(self.sinks) and self.sinks[j].group is self.sinks[i].group:
                     _, off_j, *_ = self.sinks[j].begin_push()
                     assert off_j == nxt, "fused weights must be adjacent in the flat layout"
                     rows, nxt, j = rows + self.params[j].shape[0], nxt + self.params[j].numel(), j + 1
                 if deferred is not None:
-                    deferred.append((dy[:, r0 : r0 + rows], x, off, ptrs, shard, rank, world))
+                    deferred.append((dy[:, r0 : r0 + rows], x, off, ptrs, shard, rank, world, bf16))
                 else:
                     kernels.gemm_scatter(dy[:, r0 : r0 + rows], x, a_mn_major=True, b_mn_major=True, peer_grad=ptrs, c_flat_off=off,
-                                         shard_numel=shard, rank=rank, world=world)
+                                         shard_numel=shard, rank=rank, world=world, wire_bf16=bf16)
                 i, r0 = j, r0 + rows
             return [None] * len(self.params)
-        if self.use_sinks:
+        if self.use_sinks and all(s.local_ok for s in self.sinks):
             views, accs = zip(*[s.begin() for s in self.sinks])
             fused = fuse_adjacent(list(views)) if len(views) > 1 else views[0]
             targets = [s.norm_target(acc) for s, acc in zip(self.sinks, accs)]
@@ -119,18 +119,20 @@ class _WeightGrad:
 
 
 def flush_pushed(deferred: "list[tuple[Any, ...]]") -> None:
-    """Launch the recorded weight-gradient GEMMs of a layer: one grouped, rank-rotated launch when they share the token
+    """Launch the recorded weight-gradient GEMMs of a layer: one grouped launch (owners' tiles dealt round-robin) when they share the token
     dimension and the destination (the usual case), one launch each otherwise."""
     if not deferred:
         return
     deferred.sort(key=lambda d: d[2])
-    _, _, _, ptrs, shard, rank, world = deferred[0]
+    _, _, _, ptrs, shard, rank, world, bf16 = deferred[0]
     same = all(d[3] is ptrs and d[0].shape[0] == deferred[0][0].shape[0] for d in deferred)
     if same and len(deferred) <= 4:
-        kernels.gemm_scatter_grouped([(dy, x, off) for dy, x, off, *_ in deferred], peer_grad=ptrs, shard_numel=shard, rank=rank, world=world)
+        kernels.gemm_scatter_grouped([(dy, x, off) for dy, x, off, *_ in deferred], peer_grad=ptrs, shard_numel=shard, rank=rank, world=world,
+                                     wire_bf16=bf16)
     else:
-        for dy, x, off, p, sh, r, w in deferred:
-            kernels.gemm_scatter(dy, x, a_mn_major=True, b_mn_major=True, peer_grad=p, c_flat_off=off, shard_numel=sh, rank=r, world=w)
+        for dy, x, off, p, sh, r, w, b16 in deferred:
+            kernels.gemm_scatter(dy, x, a_mn_major=True, b_mn_major=True, peer_grad=p, c_flat_off=off, shard_numel=sh, rank=r, world=w,
+                                 wire_bf16=b16)
     deferred.clear()
 
 
@@ -142,7 +144,7 @@ def _norm_weight_grad(w: torch.Tensor, fn: Any) -> torch.Tensor | None:
         fn(dw)
         s.push_from(dw)
         return None
-    if s is not None:
+    if s is not None and s.local_ok:
         zeroed_now = not s.would_accumulate()
         view, _ = s.begin(zero=True)
         fn(view)
@@ -197,7 +199,15 @@ class DecoderLayerFn(torch.autograd.Function):
         w_qkv = fuse_adjacent([wq, wk, wv])
         w_gu = fuse_adjacent([wg, wu])
         n1, rstd1 = kernels.rmsnorm_fwd(x, w_n1.detach(), dims.eps)
-        qkv = kernels.gemm(n1, w_qkv)
+        owner = getattr(wq, "_yf_group_index", None)
+        ticket = owner[0].take_in_kernel_gather(owner[1], w_qkv.shape[0]) if owner is not None else None
+        if ticket is not None:
+            # this forward pass has not gathered the layer: the QKV GEMM pulls it from the peers while it computes
+            qkv = kernels.gemm_gathered(n1, w_qkv.shape[0], w_qkv.shape[1], peer_in=ticket["peer_in"], layer_buf=ticket["layer_buf"],
+                                        shard_bytes=ticket["shard_bytes"], b_byte_off=ticket["b_byte_off"], rank=ticket["rank"],
+                                        world=ticket["world"], counters=ticket["counters"], epoch=ticket["epoch"])
+        else:
+            qkv = kernels.gemm(n1, w_qkv)
         kernels.rope_(qkv, cos_sin, dims.seq, 0, hq + hkv, hd)
         q, k, v = qkv[:, : hq * hd], qkv[:, hq * hd : (hq + hkv) * hd], qkv[:, (hq + hkv) * hd :]
         att, lse = kernels.attn_fwd(q, k, v, dims.batch, dims.seq, hq, hkv, 1.0 / math.sqrt(hd), True)

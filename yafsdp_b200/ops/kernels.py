@@ -133,7 +133,7 @@ def gemm_gathered(a: torch.Tensor, n: int, k: int, *, peer_in: Any, layer_buf: t
 
 
 def gemm_scatter(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool, b_mn_major: bool, peer_grad: Any, c_flat_off: int,
-                 shard_numel: int, rank: int, world: int, alpha: float = 1.0, sm_limit: int = 0) -> None:
+                 shard_numel: int, rank: int, world: int, alpha: float = 1.0, sm_limit: int = 0, wire_bf16: bool = False) -> None:
     """GEMM -> reduce-scatter push: the fp32 product goes piece by piece to the owners' staging slots for this rank
     (``peer_grad``: ctypes array of every rank's reduce-buffer base); nothing is stored locally."""
     m = a.shape[1] if a_mn_major else a.shape[0]
@@ -141,16 +141,16 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool, b_mn_maj
     k = a.shape[0] if a_mn_major else a.shape[1]
     rc = _native.lib().yf_gemm_bf16_scatter(a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0), b.stride(0), int(a_mn_major),
                                             int(b_mn_major), float(alpha), peer_grad, c_flat_off, shard_numel, rank, world,
-                                            int(sm_limit), _stream())
+                                            int(wire_bf16), int(sm_limit), _stream())
     _check(rc, "yf_gemm_bf16_scatter")
 
 
 def gemm_scatter_grouped(problems: list[tuple[torch.Tensor, torch.Tensor, int]], *, peer_grad: Any, shard_numel: int, rank: int,
-                         world: int, alpha: float = 1.0, sm_limit: int = 0) -> None:
+                         world: int, alpha: float = 1.0, sm_limit: int = 0, wire_bf16: bool = False) -> None:
     """The weight-gradient GEMMs of a layer as one launch pushed to their owners.  ``problems``: up to four
     ``(dy [T, out], x [T, in], flat offset of the [out, in] gradient)`` in ascending flat order; every ``dW = dy^T x``
-    goes to the owners' slots for this rank.  The tile order is rotated by rank so that the ranks push into different
-    owners at any moment."""
+    goes to the owners' slots for this rank.  The owners' tiles are dealt round-robin, so every rank pushes to all owners
+    all the time and no owner's NVLink ingress becomes a hot spot."""
     n = len(problems)
     assert 1 <= n <= 4
     k = problems[0][0].shape[0]
@@ -164,16 +164,17 @@ def gemm_scatter_grouped(problems: list[tuple[torch.Tensor, torch.Tensor, int]],
     for dy, x, _ in problems:
         assert dy.dtype == x.dtype == torch.bfloat16 and dy.shape[0] == x.shape[0] == k and dy.stride(1) == 1 and x.stride(1) == 1
     rc = _native.lib().yf_gemm_bf16_scatter_grouped(n, a_ptrs, b_ptrs, ms, ns, k, ldas, ldbs, 1, 1, float(alpha), peer_grad, offs,
-                                                    shard_numel, rank, world, int(sm_limit), _stream())
+                                                    shard_numel, rank, world, int(wire_bf16), int(sm_limit), _stream())
     _check(rc, "yf_gemm_bf16_scatter_grouped")
 
 
-def push_flat(src: torch.Tensor | None, numel: int, flat_off: int, peer_grad: Any, shard_numel: int, rank: int, world: int) -> None:
+def push_flat(src: torch.Tensor | None, numel: int, flat_off: int, peer_grad: Any, shard_numel: int, rank: int, world: int,
+              wire_bf16: bool = False) -> None:
     """Push ``numel`` fp32 values (``src``, or zeros when ``None``) that start at position ``flat_off`` of the flat layer
     gradient into the owners' reduce-scatter slots for this rank."""
     if src is not None:
         assert src.dtype == torch.float32 and src.is_contiguous() and src.numel() == numel
-    rc = _native.lib().yf_push_flat(_ptr(src), numel, flat_off, peer_grad, shard_numel, rank, world, _stream())
+    rc = _native.lib().yf_push_flat(_ptr(src), numel, flat_off, peer_grad, shard_numel, rank, world, int(wire_bf16), _stream())
     _check(rc, "yf_push_flat")
 
 

@@ -5,7 +5,7 @@
 //   S  = Q K^T          dP = dO V^T                    (fp32 in TMEM, one query row per TMEM lane)
 //   P  = exp(S*scale - lse),  dS = P * (dP - D) * scale   (softmax warps; bf16 into swizzled smem)
 //   dV += P^T dO        dK += dS^T Q                   (accumulated in TMEM over the whole walk)
-//   dQ_part = dS K      -> fp32 vector reductions into a global dQ accumulator
+//   dQ_part = dS K      -> staged in shared memory, added to a global fp32 dQ accumulator by TMA reduce-add
 // The P / dS tiles are stored once as [query][key] with the 128-byte swizzle and are read both as a
 // K-major operand (dQ) and as an MN-major operand (dV, dK): the two canonical layouts coincide.
 // D = rowsum(dO * O) comes from a small pre-pass; dQ is converted to bf16 by a post-pass.
@@ -24,7 +24,7 @@ constexpr int BKV = 128;
 constexpr int ATOM = 16384;
 constexpr int TILE = 2 * ATOM;
 constexpr int BWD_THREADS = 320;  // producer warp, MMA warp, eight softmax / epilogue warps
-constexpr int BWD_SMEM = 1024 + 6 * TILE + 256;
+constexpr int BWD_SMEM = 1024 + 7 * TILE + 256;  // K, V, Q, dO, P, dS and the dQ staging (two [128 x 32 fp32] blocks)
 
 struct BwdArgs {
   const float* lse;    // [B, Hq, S]
@@ -38,13 +38,17 @@ struct BwdArgs {
   int causal;
 };
 
-YF_DEVINL void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+YF_DEVINL void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do, BwdArgs args) {
+                const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do,
+                const __grid_constant__ CUtensorMap tma_dq, BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -53,7 +57,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint8_t* sdO = sQ + TILE;
   uint8_t* sP = sdO + TILE;
   uint8_t* sdS = sP + TILE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + TILE);
+  uint8_t* sdQ = sdS + TILE;  // two 16 KB blocks, 128-byte swizzled rows, source of the TMA reduce-adds
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdQ + TILE);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;
   uint64_t* qdo_empty = bars + 2;
@@ -177,6 +182,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const float delta = row_ok ? args.delta[stat_idx] : 0.f;
       // keys this query row may see: col <= limit
       const int limit = row_ok ? (args.causal ? min(qrow, args.S - 1) : args.S - 1) : -1;
+      const bool need_mask = kv0 + BKV - 1 > limit;
       if (!mbar_wait(sdp_full, it & 1, 220)) { alive = false; break; }
       tc_fence_after();
 #pragma unroll 1
@@ -188,10 +194,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int t = 0; t < 32; t += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(rs[t]), sl2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(rs[t + 1]), sl2, -lse2));
-          if (kv0 + c * 32 + t > limit) p0 = 0.f;
-          if (kv0 + c * 32 + t + 1 > limit) p1 = 0.f;
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[t]), sl2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[t + 1]), sl2, -lse2));
+          if (need_mask) {  // only the tiles on the diagonal and the last one have masked keys
+            if (kv0 + c * 32 + t > limit) p0 = 0.f;
+            if (kv0 + c * 32 + t + 1 > limit) p1 = 0.f;
+          }
           const float d0 = p0 * (__uint_as_float(rp[t]) - delta) * args.scale;
           const float d1 = p1 * (__uint_as_float(rp[t + 1]) - delta) * args.scale;
           pk[t >> 1] = pack_bf16x2(p0, p1);
@@ -210,22 +218,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       mbar_arrive(pds_ready);
       if (!mbar_wait(dq_full, it & 1, 221)) { alive = false; break; }
       tc_fence_after();
-      float* dq_row = args.dq_accum + ((long long)b * args.S + qrow) * ((long long)args.Hq * HD) + h * HD;
+      // dQ_part: TMEM -> registers -> swizzled staging block -> one TMA reduce-add per [128 rows x 32 columns] block (full
+      // 128-byte lines reach the L2 reduction units; rows past the end of the sequence are clipped by the tensor map).
+      // The two column halves of the tile use one staging block each; two passes cover the four 32-column chunks.
+      const bool dq_thread = (threadIdx.x == 64 || threadIdx.x == 64 + 128);  // first thread of each half
 #pragma unroll 1
-      for (int c = c_begin; c < c_end; ++c) {
+      for (int pass = 0; pass < 2; ++pass) {
+        const int c = c_begin + pass;
+        uint8_t* blk = sdQ + (c_begin >> 1) * ATOM;  // half 0 -> block 0, half 1 -> block 1
         uint32_t r[32];
         tmem_ld32(tS + lane_off + c * 32, r);
         tmem_ld_wait();
-        if (row_ok) {
+        if (dq_thread) tma_store_wait_read0();  // the reduce that last read this block has finished reading
+        named_bar_sync(2 + (c_begin >> 1), 128);
+        uint8_t* srow = blk + row * 128;
 #pragma unroll
-          for (int t = 0; t < 32; t += 4)
-            red_add_v4(dq_row + c * 32 + t, __uint_as_float(r[t]), __uint_as_float(r[t + 1]), __uint_as_float(r[t + 2]),
-                       __uint_as_float(r[t + 3]));
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        fence_proxy_async_smem();
+        named_bar_sync(2 + (c_begin >> 1), 128);
+        if (dq_thread) {
+          tma_reduce_add_3d(&tma_dq, blk, h * HD + c * 32, q0, b);
+          tma_store_commit();
         }
       }
       tc_fence_before();
       mbar_arrive(dq_read);
     }
+    if (threadIdx.x == 64 || threadIdx.x == 64 + 128) tma_store_wait0();  // this thread's dQ reduce-adds have completed
     // dK, dV: TMEM lane == key row.  The last dq_full wait covers every MMA issued before it.
     if (alive) {  // every lane issues the (warp-collective) TMEM loads; only the stores are predicated
       const bool key_ok = kv0 + row < args.S;
@@ -308,7 +328,8 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
 
 // The three launches of one backward pass (delta pre-pass, main kernel, dQ conversion), shared by both entry points.
 // Allocates nothing: the tensor maps come by reference from the caller, the scratch by pointer.
-static int attn_bwd_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md, const void* out,
+static int attn_bwd_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md,
+                           const CUtensorMap& mdq, const void* out,
                            const void* dout, const float* lse, float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B,
                            int S, int Hq, int Hkv, long long o_stride, long long do_stride, long long dq_stride,
                            long long dkv_stride, float scale, int causal, cudaStream_t st) {
@@ -344,7 +365,7 @@ static int attn_bwd_launch(const CUtensorMap& mq, const CUtensorMap& mk, const C
   a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal ? 1 : 0;
   dim3 grid((S + BKV - 1) / BKV, Hkv, B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, md, a);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(mq, mk, mv, md, mdq, a);
   {
     const long long items = T * (Hq * HD / 8);
     long long blocks = (items + 255) / 256;
@@ -374,8 +395,9 @@ extern "C" int yf_attn_bwd(const void* q, const void* k, const void* v, const vo
   const CUtensorMap* mk = yf_tensor_map_3d(k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
   const CUtensorMap* mv = yf_tensor_map_3d(v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1);
   const CUtensorMap* md = yf_tensor_map_3d(dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1);
-  if (!mq || !mk || !mv || !md) return -2;
-  return attn_bwd_launch(*mq, *mk, *mv, *md, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
+  const CUtensorMap* mdq = yf_tensor_map_3d(dq_accum, (uint64_t)Hq * HD, S, B, (uint64_t)Hq * HD, (uint64_t)S * Hq * HD, 32, BQ, 1, 4, 1);
+  if (!mq || !mk || !mv || !md || !mdq) return -2;
+  return attn_bwd_launch(*mq, *mk, *mv, *md, *mdq, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
                          dkv_stride, scale, causal, st);
 }
 
@@ -451,12 +473,13 @@ extern "C" int yf_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
   float* delta = scratch;
   float* dq_accum = scratch + NOALLOC_DELTA_FLOATS;  // 131072 bytes in: still 256-byte aligned
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  CUtensorMap mq, mk, mv, md;  // encoded in place: the cached variants would allocate a cache entry
+  CUtensorMap mq, mk, mv, md, mdq;  // encoded in place: the cached variants would allocate a cache entry
   if (yf_tensor_map_3d_encode(&mq, q, (uint64_t)Hq * HD, S, B, q_stride, (uint64_t)S * q_stride, 64, BQ, 1, 2, 1) != 0 ||
       yf_tensor_map_3d_encode(&mk, k, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1) != 0 ||
       yf_tensor_map_3d_encode(&mv, v, (uint64_t)Hkv * HD, S, B, kv_stride, (uint64_t)S * kv_stride, 64, BKV, 1, 2, 1) != 0 ||
-      yf_tensor_map_3d_encode(&md, dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1) != 0)
+      yf_tensor_map_3d_encode(&md, dout, (uint64_t)Hq * HD, S, B, do_stride, (uint64_t)S * do_stride, 64, BQ, 1, 2, 1) != 0 ||
+      yf_tensor_map_3d_encode(&mdq, dq_accum, (uint64_t)Hq * HD, S, B, (uint64_t)Hq * HD, (uint64_t)S * Hq * HD, 32, BQ, 1, 4, 1) != 0)
     return -2;
-  return attn_bwd_launch(mq, mk, mv, md, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
+  return attn_bwd_launch(mq, mk, mv, md, mdq, out, dout, lse, delta, dq_accum, dq, dk, dv, B, S, Hq, Hkv, o_stride, do_stride, dq_stride,
                          dkv_stride, scale, causal, st);
 }

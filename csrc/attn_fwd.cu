@@ -6,7 +6,11 @@
 //   warps 2-9  softmax:      two threads per query row (TMEM lane == row; the pair splits the 128 key columns and
 //                            the 128 output columns, and exchanges its partial row maximum through shared
 //                            memory): online max / sum, P written as bf16 into 128-byte-swizzled shared memory
-//                            (the A operand of the second MMA), running output kept in registers and rescaled.
+//                            (the A operand of the second MMA).
+// The output accumulates in TMEM over all key blocks (O += P V).  The exponent's reference maximum is only moved when
+// some row's maximum has grown by more than 2^8 since it was set (then every row rescales its O in TMEM and its sum);
+// otherwise P is taken relative to the older maximum (values up to 2^8, harmless in bf16 / fp32), the softmax of block
+// j+1 does not wait for the MMA of block j, and the final division by the row sum makes the result exact again.
 // Inputs are read in place from the fused QKV projection output ([tokens, (Hq+2Hkv)*128], row pitch
 // given), so no head transposes are materialised.  Writes O (bf16) and the log-sum-exp per row (fp32).
 #include "common.cuh"
@@ -142,7 +146,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           tc_mma_bf16(tmem_O, umma_smem_desc_sw128(aP + (k >> 2) * ATOM + (k & 3) * 32, 0, 1024),
-                      umma_smem_desc_sw128(aV + k * 2048, ATOM, 1024), idesc_o, k != 0);
+                      umma_smem_desc_sw128(aV + k * 2048, ATOM, 1024), idesc_o, (j | k) != 0);  // O accumulates over the blocks
         }
         tc_commit(o_full);
         tc_commit(&kv_empty[s]);
@@ -154,11 +158,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const int half = (warp - 2) >> 2;        // which 64 key columns / 64 output columns of the row this thread owns
     const int c_begin = half * 2;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    float o[HD / 2];
-#pragma unroll
-    for (int i = 0; i < HD / 2; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;    // l_run: this thread's half of the row sum
+    float m_run = -INFINITY, l_run = 0.f;    // m_run: reference maximum of the exponent; l_run: this thread's half of the row sum
     const float sl2 = args.scale_log2;
+    constexpr float RESCALE_LOG2 = 8.f;      // move the reference maximum when a row's maximum exceeds it by 2^8
     bool alive = true;
     bool gave_up = false;  // this thread's bounded wait ran out: all 256 softmax threads leave together at the next barrier
     for (int j = 0; j < n_kv && alive; ++j) {
@@ -169,19 +171,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       // keys allowed for this row: col <= limit
       const int limit = args.causal ? min(q0 + row, args.S - 1) : (args.S - 1);
       const bool need_mask = (kv0 + BKV - 1 > limit);
+      // this thread's 64 scores, read from TMEM once
+      uint32_t sc[2][32];
+      tmem_ld32(ts + c_begin * 32, sc[0]);
+      tmem_ld32(ts + (c_begin + 1) * 32, sc[1]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = c_begin; c < c_begin + 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(ts + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t)
-            if (kv0 + c * 32 + t <= limit) mx = fmaxf(mx, __uint_as_float(r[t]));
-        } else {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
+        for (int t = 0; t < 32; ++t) {
+          const bool ok = !need_mask || (kv0 + (c_begin + c) * 32 + t <= limit);
+          if (ok) mx = fmaxf(mx, __uint_as_float(sc[c][t]));
         }
       }
       // combine with the partner thread's half (buffers alternate with the block parity: one barrier per block)
@@ -189,51 +190,76 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       xm[half * 128 + row] = mx;
       if (named_bar_or(2, 256, gave_up)) { alive = false; break; }  // the barrier of the maximum exchange carries the give-up flag
       mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * sl2);
+      // does any row of the tile need a new reference maximum?  (uniform over all softmax threads: they share TMEM loads)
+      const bool grew = (j == 0) || (mx != -INFINITY && (m_run == -INFINITY || (mx - m_run) * sl2 > RESCALE_LOG2));
+      if (named_bar_or(3, 256, grew)) {
+        const float m_new = fmaxf(m_run, mx);
+        if (j > 0) {
+          // O holds sums relative to the old maximum: wait for the last P V to land, then scale this thread's 64 columns
+          if (!mbar_wait(o_full, (j - 1) & 1, 121)) gave_up = true;
+          tc_fence_after();
+          const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem_O + lane_off + (c_begin + c) * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) r[t] = __float_as_uint(__uint_as_float(r[t]) * alpha);
+            tmem_st32(tmem_O + lane_off + (c_begin + c) * 32, r);
+          }
+          tmem_st_wait();
+          l_run *= alpha;
+        }
+        m_run = m_new;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_ms = -m_use * sl2;
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = c_begin; c < c_begin + 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(ts + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      uint32_t packed[2][16];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int t = 0; t < 32; t += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[t]), sl2, neg_ms));
-          float p1 = exp2f(fmaf(__uint_as_float(r[t + 1]), sl2, neg_ms));
+          float p0 = fast_exp2(fmaf(__uint_as_float(sc[c][t]), sl2, neg_ms));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sc[c][t + 1]), sl2, neg_ms));
           if (need_mask) {
-            if (kv0 + c * 32 + t > limit) p0 = 0.f;
-            if (kv0 + c * 32 + t + 1 > limit) p1 = 0.f;
+            if (kv0 + (c_begin + c) * 32 + t > limit) p0 = 0.f;
+            if (kv0 + (c_begin + c) * 32 + t + 1 > limit) p1 = 0.f;
           }
           rowsum += p0 + p1;
-          packed[t >> 1] = pack_bf16x2(p0, p1);
-        }
-        uint8_t* prow = sP + (c >> 1) * ATOM + row * 128;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int chunk = (c & 1) * 4 + t;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+          packed[c][t >> 1] = pack_bf16x2(p0, p1);
         }
       }
-      l_run = l_run * alpha + rowsum;
-      m_run = m_new;
+      l_run += rowsum;
+      // the P buffer is free once the previous block's P V has read it; by now that MMA has had the whole softmax to finish
+      if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, 122)) gave_up = true;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int cc = c_begin + c;
+        uint8_t* prow = sP + (cc >> 1) * ATOM + row * 128;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int chunk = (cc & 1) * 4 + t;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(packed[c][4 * t], packed[c][4 * t + 1], packed[c][4 * t + 2], packed[c][4 * t + 3]);
+        }
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
-      if (!mbar_wait(o_full, j & 1, 121)) gave_up = true;  // taken by everybody at the next block's barrier (or below)
-      tc_fence_after();
+    }
+    // the output of the last block
+    if (alive && n_kv > 0 && !mbar_wait(o_full, (n_kv - 1) & 1, 123)) gave_up = true;
+    tc_fence_after();
+    float o[HD / 2];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_O + lane_off + (c_begin + c) * 32, r);
-        tmem_ld_wait();
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem_O + lane_off + (c_begin + c) * 32, r);
+      tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < 32; ++t) o[c * 32 + t] = fmaf(o[c * 32 + t], alpha, __uint_as_float(r[t]));
-      }
+      for (int t = 0; t < 32; ++t) o[c * 32 + t] = __uint_as_float(r[t]);
     }
     // total row sum = both halves
     xsum[half * 128 + row] = l_run;

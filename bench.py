@@ -225,6 +225,18 @@ def run(args, make_step) -> dict:
     return result
 
 
+def resolve_reshard(args, world: int) -> bool:
+    """``--reshard-after-forward auto`` (both arms alike): layers keep their gathered bf16 parameters between forward and
+    backward (one all-gather per layer and step instead of two) when the whole bf16 model fits beside the sharded plan in
+    60 % of a B200's memory, else they are freed after forward and gathered again for backward."""
+    if args.reshard_after_forward != "auto":
+        return args.reshard_after_forward == "true"
+    from yafsdp_b200.models.llama import CONFIGS
+    from yafsdp_b200.utils.memory import keep_gathered_fits
+
+    return not keep_gathered_fits(CONFIGS[args.model], world, args.seq_len, args.batch, args.checkpoint_layers)
+
+
 # ----------------------------------------------------------------------------------------- ours
 def make_step_ours(args, rank: int, world: int, device: torch.device):
     from yafsdp_b200.models.llama import CONFIGS
@@ -233,7 +245,9 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
     from yafsdp_b200.train import TrainStep, build_llama
 
     cfg = CONFIGS[args.model]
-    model = build_llama(cfg, device, comm_backend=args.comm_backend, checkpoint_layers=args.checkpoint_layers)
+    reshard = resolve_reshard(args, world)
+    model = build_llama(cfg, device, comm_backend=args.comm_backend, checkpoint_layers=args.checkpoint_layers,
+                        reshard_after_forward=reshard)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, device)
 
@@ -252,7 +266,7 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
             dist.barrier()
             be.dry_run = on
 
-    detail = {"comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join}
+    detail = {"comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join, "reshard_after_forward": reshard}
     if backend == "symm":
         detail["_dry_run"] = dry_run
     return step_dev, step_e2e, cfg.vocab_size, kernels.launch_count, detail
@@ -291,7 +305,8 @@ def make_step_reference(args, rank: int, world: int, device: torch.device):
     # an inplace operation").  Its public `reshard_after_forward=False` gives every group its own buffer and
     # skips the backward re-gather, which runs; with one rank there is no communication either way.
     kw = dict(mesh=mesh, mp_policy=mp)
-    if world == 1:
+    reshard = resolve_reshard(args, world)  # the same rule as in the other arm
+    if world == 1 or not reshard:
         kw["reshard_after_forward"] = False
     if args.checkpoint_layers:
         # the reference's recipe: non-reentrant activation checkpointing on the first N decoder layers, applied before sharding
@@ -324,7 +339,7 @@ def make_step_reference(args, rank: int, world: int, device: torch.device):
 
     return step_dev, step_e2e, c.vocab_size, (lambda: 0), {
         "attn_implementation": attn_impl, "params": c.num_params(), "model_code": "transformers.LlamaForCausalLM",
-        "reshard_after_forward": world != 1}
+        "reshard_after_forward": world != 1 and reshard}
 
 
 def main() -> None:
@@ -339,6 +354,8 @@ def main() -> None:
     ap.add_argument("--comm-backend", default="auto", choices=["auto", "torch", "symm"])
     ap.add_argument("--ref-attn", default="sdpa", choices=["sdpa", "flash_attention_2", "eager"])
     ap.add_argument("--checkpoint-layers", type=int, default=0, help="activation checkpointing on the first N decoder layers")
+    ap.add_argument("--reshard-after-forward", default="auto", choices=["auto", "true", "false"],
+                    help="free the gathered parameters after forward (true), keep them until backward (false), or keep them when they fit (auto)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

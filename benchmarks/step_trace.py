@@ -78,7 +78,7 @@ def summarize(trace_path: str, world: int, steps: int) -> str:
 def _load_kernels(path: str) -> list:
     with (gzip.open(path) if path.endswith(".gz") else open(path, "rb")) as f:
         d = json.load(f)
-    ev = [e for e in d["traceEvents"] if e.get("cat") == "kernel" and "dur" in e]
+    ev = [e for e in d["traceEvents"] if e.get("cat") in ("kernel", "gpu_memcpy") and "dur" in e]
     ev.sort(key=lambda e: e["ts"])
     return ev
 
@@ -89,7 +89,8 @@ def overlap_report(trace_path: str, baseline_path: str | None, steps: int) -> st
     ev = _load_kernels(trace_path)
     is_gemm = lambda e: "gemm_bf16" in e["name"]  # noqa: E731
     gemms = [e for e in ev if is_gemm(e)]
-    ag = [e for e in ev if "allgather" in e["name"]]
+    # the all-gather is a kernel (pull / multicast transports) or peer copies on the copy engines
+    ag = [e for e in ev if "allgather" in e["name"] or (e.get("cat") == "gpu_memcpy" and ("PtoP" in e["name"] or "DtoD" in e["name"]) and e["dur"] > 50)]
     rs = [e for e in ev if "reduce_scatter" in e["name"]]
     per = len(gemms) // steps
     last = gemms[-per:]
@@ -139,7 +140,10 @@ def main() -> None:
     os.environ.setdefault("MASTER_PORT", "29655")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = CONFIGS[args.model]
-    model = build_llama(cfg, dev, comm_backend="symm" if world > 1 else "auto")
+    from yafsdp_b200.utils.memory import keep_gathered_fits
+
+    keep = keep_gathered_fits(cfg, world, args.seq_len)  # the rule bench.py applies: keep the gathered weights when they fit
+    model = build_llama(cfg, dev, comm_backend="symm" if world > 1 else "auto", reshard_after_forward=not keep)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, dev)
     ids = torch.randint(0, cfg.vocab_size, (1, args.seq_len), device=dev)

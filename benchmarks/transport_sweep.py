@@ -7,7 +7,8 @@ The model is built once (multicast arena when the box has NVSwitch multicast), t
 measurements with ``SymmBackend.set_transports``: a configuration costs a few steps, not a start-up.  A configuration is
 ``<all-gather>[:CTAs]/<reduce-scatter>[:CTAs][+1s]`` with transports ``ce`` (copy engines), ``sm`` (pull kernels),
 ``mc`` (NVSwitch multicast); ``+1s`` puts both collectives on one communication stream, ``+fr`` fuses the gradient
-reduce-scatter into the weight-gradient GEMMs (rows pushed to their owners from the epilogue).  The configuration ``dry``
+reduce-scatter into the weight-gradient GEMMs (rows pushed to their owners from the epilogue), ``+fg`` lets the first
+layer gather inside its QKV GEMM, ``+rs`` (with ``--keep-gathered``) frees the parameters after forward as usual.  The configuration ``dry``
 times the step with collectives that move nothing (compute-only step at this world size); put it last.  Rank 0 prints one JSON line per
 configuration: CUDA-event time of ``--steps`` steps, max over ranks.
 """
@@ -43,13 +44,17 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--configs", default=DEFAULT)
     ap.add_argument("--checkpoint-layers", type=int, default=0)
+    ap.add_argument("--keep-gathered", action="store_true",
+                    help="give every layer its own gather buffer (reshard_after_forward=False); the flag '+rs' of a configuration then "
+                         "frees and re-gathers as usual, configurations without it keep the parameters from forward to backward")
     a = ap.parse_args()
     rank, world, dev = init_distributed("cuda")
     if world < 2:
         raise SystemExit("transport_sweep needs at least 2 ranks")
     cfg = CONFIGS[a.model]
     wants_mc = "mc" in a.configs
-    model = build_llama(cfg, dev, comm_backend="symm", checkpoint_layers=a.checkpoint_layers, multicast=wants_mc)
+    model = build_llama(cfg, dev, comm_backend="symm", checkpoint_layers=a.checkpoint_layers, multicast=wants_mc,
+                        reshard_after_forward=not a.keep_gathered)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, dev)
     ids = torch.randint(0, cfg.vocab_size, (1, a.seq_len), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
@@ -65,6 +70,13 @@ def main() -> None:
             spec_run = spec
         flags = spec_run.split("+")[1:]
         single, fused = "1s" in flags, "fr" in flags
+        first = model.model.layers[0]
+        first.set_fused_gather("fg" in flags, prefix_params=[first.input_layernorm.weight])  # '+fg': layer 0 gathers inside its QKV GEMM
+        if a.keep_gathered:
+            from yafsdp_b200.optim import param_groups_of
+
+            for g in param_groups_of(model):
+                g.reshard_after_forward = "rs" in flags
         body = spec_run.split("+")[0]
         ag_s, rs_s = body.split("/")
         ag_p, rs_p = ag_s.split(":"), rs_s.split(":")

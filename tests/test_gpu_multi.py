@@ -122,7 +122,7 @@ def _train_worker(rank, world):
     ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
     losses = {}
     for backend in ("torch", "symm"):
-        model = build_llama(cfg, dev, comm_backend=backend)
+        model = build_llama(cfg, dev, comm_backend=backend, fused_gather=True)
         opt = ShardedAdamW(model, lr=1e-3, max_grad_norm=1.0)
         step = TrainStep(model, opt, dev)
         losses[backend] = [step(ids).item() for _ in range(4)]

@@ -188,8 +188,9 @@ class SymmBackend(CommBackend):
 
     N_SLOTS = 8
     SLOT_STEP, SLOT_RS_READY, SLOT_RS_DONE, SLOT_SYNC, SLOT_MC_PRE, SLOT_MC_POST = 0, 1, 2, 3, 4, 5
-    #: measured on 8 x B200 (Llama-2-7B step): all-gather on the copy engines at every world size
-    DEFAULT_TRANSPORTS = {"ag": lambda world: "ce", "rs": lambda world: "ce" if world <= 4 else "sm"}
+    #: measured on 2 and 8 x B200 (Llama-2-7B step, ``benchmarks/transport_sweep.py``): all-gather on the copy engines,
+    #: reduce-scatter by the pull kernel, at every world size
+    DEFAULT_TRANSPORTS = {"ag": lambda world: "ce", "rs": lambda world: "sm"}
 
     def __init__(self, device: torch.device, group: dist.ProcessGroup | None, *, ag_transport: str | None = None,
                  rs_transport: str | None = None, multicast: bool | None = None, ag_ctas: int = 0, rs_ctas: int = 0,

@@ -260,14 +260,19 @@ def shard_llama(model: LlamaForCausalLM, *, mesh: Any = None, mp_policy: MixedPr
     fully_shard([model.model.norm, model.lm_head], **kw)
     fully_shard(model, **kw)
     if fused_gather is None:
-        fused_gather = os.environ.get("YAFSDP_FUSED_GATHER", "1") == "1"
+        fused_gather = os.environ.get("YAFSDP_FUSED_GATHER", "0") == "1"
     if fused_gather and len(model.model.layers) > 0:
         # the first layer's gather is the one nothing can hide (the step starts with it): its QKV GEMM pulls the layer itself;
         # every later layer's gather is issued ahead of time on the communication stream
         first = model.model.layers[0]
         first.set_fused_gather(True, prefix_params=[first.input_layernorm.weight])  # type: ignore[attr-defined]
     if fused_reduce is None:
-        fused_reduce = os.environ.get("YAFSDP_FUSED_REDUCE", "0") == "1"
+        # measured (Llama-2-7B step): at two ranks the pushed gradients ride under the weight-gradient GEMMs (NVLink time
+        # below GEMM time) and the step gets 1.5 % shorter; from four ranks on the push is link-bound and the overlapped
+        # reduce-scatter wins.  YAFSDP_FUSED_REDUCE=0/1 overrides.
+        env = os.environ.get("YAFSDP_FUSED_REDUCE")
+        world = mesh.size() if mesh is not None else (torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1)
+        fused_reduce = (env == "1") if env is not None else world == 2
     if fused_reduce:
         # decoder layers and the head use every weight once per backward pass: their weight-gradient GEMMs push straight to
         # the owners (the embedding's gradient comes from a scatter-add kernel and stays on the unfused path)

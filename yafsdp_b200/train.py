@@ -49,14 +49,16 @@ def init_distributed(device_type: str | None = None) -> tuple[int, int, torch.de
 
 def build_llama(cfg: LlamaConfig, device: torch.device, *, seed: int = 0, comm_backend: Any = "auto", checkpoint_layers: int = 0,
                 mp_policy: MixedPrecisionPolicy | None = None, num_grad_buffers: int = 2, mesh: Any = None,
-                fused_reduce: bool | None = None, fused_gather: bool | None = None, **backend_options: Any) -> LlamaForCausalLM:
+                fused_reduce: bool | None = None, fused_gather: bool | None = None, reshard_after_forward: bool | None = True,
+                **backend_options: Any) -> LlamaForCausalLM:
     from torch.distributed.device_mesh import init_device_mesh
 
     if mesh is None:
         mesh = init_device_mesh(device.type, (dist.get_world_size(),))
     with torch.device("meta"):
         model = LlamaForCausalLM(cfg)
-    shard_llama(model, mesh=mesh, mp_policy=mp_policy, comm_backend=comm_backend, num_grad_buffers=num_grad_buffers,
+    shard_llama(model, mesh=mesh, mp_policy=mp_policy, reshard_after_forward=reshard_after_forward, comm_backend=comm_backend,
+                num_grad_buffers=num_grad_buffers,
                 checkpoint_layers=checkpoint_layers, fused_reduce=fused_reduce, fused_gather=fused_gather, **backend_options)
     model.init_weights(seed)
     return model

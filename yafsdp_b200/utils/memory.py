@@ -18,7 +18,7 @@ from __future__ import annotations
 
 from typing import Any
 
-__all__ = ["estimate_memory", "B200_HBM_BYTES"]
+__all__ = ["estimate_memory", "keep_gathered_fits", "B200_HBM_BYTES"]
 
 B200_HBM_BYTES = 183_359 * 2**20  # what nvidia-smi reports for a B200
 
@@ -43,3 +43,14 @@ def estimate_memory(cfg: Any, world: int, seq_len: int, batch: int = 1, checkpoi
     total = state + buffers + activations + logits
     return {"state": state, "buffers": buffers, "activations": activations, "logits": logits, "total": total,
             "fits": float(total < 0.95 * B200_HBM_BYTES)}
+
+
+def keep_gathered_fits(cfg: Any, world: int, seq_len: int, batch: int = 1, checkpoint_layers: int = 0, num_grad_buffers: int = 2,
+                       budget_fraction: float = 0.6) -> bool:
+    """Can every layer keep its gathered bf16 parameters from its forward to its backward pass (``reshard_after_forward=
+    False``: one gather per layer and step instead of two) within ``budget_fraction`` of a B200's memory?  The whole
+    compute-dtype model then sits on every GPU during a step (2 bytes per parameter) on top of the sharded plan."""
+    if world <= 1:
+        return False  # single rank: the shards are the parameters, nothing is gathered
+    plan = estimate_memory(cfg, world, seq_len, batch, checkpoint_layers, num_grad_buffers)
+    return plan["total"] + 2.0 * cfg.num_params() <= budget_fraction * B200_HBM_BYTES

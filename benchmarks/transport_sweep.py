@@ -44,6 +44,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--configs", default=DEFAULT)
     ap.add_argument("--checkpoint-layers", type=int, default=0)
+    ap.add_argument("--num-grad-buffers", type=int, default=2, help="rotating fp32 gradient buffers (reduce-scatter inputs)")
     ap.add_argument("--keep-gathered", action="store_true",
                     help="give every layer its own gather buffer (reshard_after_forward=False); the flag '+rs' of a configuration then "
                          "frees and re-gathers as usual, configurations without it keep the parameters from forward to backward")
@@ -54,7 +55,7 @@ def main() -> None:
     cfg = CONFIGS[a.model]
     wants_mc = "mc" in a.configs
     model = build_llama(cfg, dev, comm_backend="symm", checkpoint_layers=a.checkpoint_layers, multicast=wants_mc,
-                        reshard_after_forward=not a.keep_gathered)
+                        reshard_after_forward=not a.keep_gathered, num_grad_buffers=a.num_grad_buffers)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, dev)
     ids = torch.randint(0, cfg.vocab_size, (1, a.seq_len), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
@@ -108,7 +109,7 @@ def main() -> None:
         t = torch.tensor([s.elapsed_time(e) / a.steps], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
-            print(json.dumps({"config": spec, "world": world, "ms_per_step": round(float(t.item()), 2), "loss": round(float(loss.item()), 4),
+            print(json.dumps({"config": spec, "keep_gathered": a.keep_gathered, "grad_buffers": a.num_grad_buffers, "world": world, "ms_per_step": round(float(t.item()), 2), "loss": round(float(loss.item()), 4),
                               "tokens_per_s": round(world * a.seq_len / float(t.item()) * 1e3, 1)}), flush=True)
     dist.destroy_process_group()
 

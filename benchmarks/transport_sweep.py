@@ -6,7 +6,7 @@
 The model is built once (multicast arena when the box has NVSwitch multicast), then the transports are switched between
 measurements with ``SymmBackend.set_transports``: a configuration costs a few steps, not a start-up.  A configuration is
 ``<all-gather>[:CTAs]/<reduce-scatter>[:CTAs][+1s]`` with transports ``ce`` (copy engines), ``sm`` (pull kernels),
-``mc`` (NVSwitch multicast); ``+1s`` puts both collectives on one communication stream, ``+fr`` fuses the gradient
+``mc`` (NVSwitch multicast), ``cp`` (all-gather only: copy engines writing to the peers); ``+1s`` puts both collectives on one communication stream, ``+fr`` fuses the gradient
 reduce-scatter into the weight-gradient GEMMs (rows pushed to their owners from the epilogue), ``+fg`` lets the first
 layer gather inside its QKV GEMM, ``+rs`` (with ``--keep-gathered``) frees the parameters after forward as usual.  The configuration ``dry``
 times the step with collectives that move nothing (compute-only step at this world size); put it last.  Rank 0 prints one JSON line per
@@ -55,7 +55,7 @@ def main() -> None:
     cfg = CONFIGS[a.model]
     wants_mc = "mc" in a.configs
     model = build_llama(cfg, dev, comm_backend="symm", checkpoint_layers=a.checkpoint_layers, multicast=wants_mc,
-                        reshard_after_forward=not a.keep_gathered, num_grad_buffers=a.num_grad_buffers)
+                        symmetric_gather_output="cp" in a.configs, reshard_after_forward=not a.keep_gathered, num_grad_buffers=a.num_grad_buffers)
     opt = ShardedAdamW(model, lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
     step = TrainStep(model, opt, dev)
     ids = torch.randint(0, cfg.vocab_size, (1, a.seq_len), generator=torch.Generator().manual_seed(1 + rank)).to(dev)

@@ -56,6 +56,10 @@ struct GemmArgs {
   long long ldc;
   float alpha;
   int a_mn, b_mn, out_f32, accumulate;
+  // optional bf16 residual [M, N] with row pitch ldr, added in fp32 before the bf16 output is rounded (bf16 output, plain
+  // mode): a block's "x + proj(...)" costs no pass of its own over the activations
+  const void* R;
+  long long ldr;
   // Grouped launch (scatter mode): n_prob problems that share K and the operand majors, in the order of their positions in
   // the flat layer gradient.  Tiles are numbered problem by problem, rows first (= in flat order); tile_prefix[p] = number
   // of tiles in front of problem p; own_start[o] = first tile whose rows begin in the shard of rank o.  The launch deals the
@@ -572,17 +576,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GroupMaps maps, const __grid_co
         } else {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
+            // the residual of this thread's row: 4 x 16 bytes, requested before the accumulator is read (N % 8 == 0)
+            uint4 res[4] = {};
+            if (args.R != nullptr) {
+              const int row = m0 + r_in_tile, col = n0 + c * 64 + half * 32;
+              if (row < M) {
+                const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (col + 8 * j < N) res[j] = __ldg(rp + j);
+              }
+            }
             uint32_t r[32];
             tmem_ld32(taddr + c * 64 + half * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              uint4 o;
-              o.x = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 0]), alpha * __uint_as_float(r[8 * j + 1]));
-              o.y = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 2]), alpha * __uint_as_float(r[8 * j + 3]));
-              o.z = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 4]), alpha * __uint_as_float(r[8 * j + 5]));
-              o.w = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 6]), alpha * __uint_as_float(r[8 * j + 7]));
-              *reinterpret_cast<uint4*>(srow + (((half * 4 + j) ^ (r_in_tile & 7)) << 4)) = o;
+              const uint32_t rw[4] = {res[j].x, res[j].y, res[j].z, res[j].w};
+              uint32_t ow[4];
+#pragma unroll
+              for (int w = 0; w < 4; ++w)  // a bf16 pair: low half = even column
+                ow[w] = pack_bf16x2(fmaf(alpha, __uint_as_float(r[8 * j + 2 * w]), __uint_as_float(rw[w] << 16)),
+                                    fmaf(alpha, __uint_as_float(r[8 * j + 2 * w + 1]), __uint_as_float(rw[w] & 0xffff0000u)));
+              *reinterpret_cast<uint4*>(srow + (((half * 4 + j) ^ (r_in_tile & 7)) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
             }
           }
         }
@@ -795,6 +811,28 @@ extern "C" int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, 
   memset(&fa, 0, sizeof(fa));
   fa.sumsq = sumsq;
   return dispatch_gemm(A, B, args, fa, lda, ldb, sm_limit, s);
+}
+
+// C[M,N] = alpha * A * B^T + R with a bf16 residual R [M,N] (row pitch ldr) added in fp32 before the bf16 output is rounded;
+// C may be R itself.  N, ldr multiples of 8; R 16-byte aligned.
+extern "C" int yf_gemm_bf16_residual(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, float alpha, int sm_limit,
+                                     void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || R == nullptr) return -1;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (ldr % 8) || (N % 8) || (reinterpret_cast<uintptr_t>(R) & 15)) return -1;
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.C = C;
+  args.M = M; args.N = N; args.K = K;
+  args.ldc = ldc;
+  args.alpha = alpha;
+  args.a_mn = a_mn ? 1 : 0;
+  args.b_mn = b_mn ? 1 : 0;
+  args.R = R;
+  args.ldr = ldr;
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  return dispatch_gemm(A, B, args, fa, lda, ldb, sm_limit, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // All-gather -> GEMM in one kernel.  C[M,N] = A[M,K] * B[N,K]^T where B (row-major, contiguous, K-major) is a

@@ -21,6 +21,9 @@ int yf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
 int yf_gemm_bf16_sumsq(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, float alpha, int sm_limit, float* sumsq,
                        void* stream);
+/* C = alpha * A * B^T + R: bf16 output, bf16 residual R [M,N] (row pitch ldr) added in fp32 in the epilogue; C may be R. */
+int yf_gemm_bf16_residual(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, long long ldr, int a_mn, int b_mn, float alpha, int sm_limit, void* stream);
 // fused all-gather -> GEMM and GEMM -> reduce-scatter (same kernel, see gemm.cu for the argument contracts)
 int yf_gemm_bf16_gathered(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int a_mn, int out_f32,
                           void* const* peer_in, void* layer_buf, long long shard_bytes, long long b_byte_off, int rank, int world,

@@ -79,3 +79,28 @@ def test_gemm_fused_sum_of_squares():
     kernels.check_status()
     want = 5.0 + out.double().pow(2).sum().item()
     assert abs(acc.item() - want) <= 1e-4 * want
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (200, 328, 136), (2048, 4096, 1024), (448, 1000, 136), (130, 136, 64)])
+def test_gemm_residual_epilogue(m, n, k):
+    """out = A @ B^T + R with the bf16 residual added in fp32 inside the epilogue (single-CTA and CTA-pair tiles, ragged
+    edges, a residual with a row pitch, and in place on the residual)."""
+    from yafsdp_b200.ops import kernels
+
+    torch.manual_seed(3)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    wide = (8 * torch.randn(m, n + 24, device="cuda")).bfloat16()
+    res = wide[:, 8 : 8 + n]  # 16-byte aligned view with a pitch of n + 24
+    ref = a.float() @ b.float().t() + res.float()
+    out = kernels.gemm(a, b, residual=res)
+    torch.cuda.synchronize()
+    kernels.check_status()
+    scale = ref.abs().max().item()
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * scale + 1e-2
+    # one rounding only: no worse than rounding the exact sum to bf16, up to the accumulation order
+    assert (out.float() - ref).abs().max().item() <= (ref.bfloat16().float() - ref).abs().max().item() + 1e-3 * scale
+    inplace = res.contiguous()
+    kernels.gemm(a, b, residual=inplace, out=inplace)
+    torch.cuda.synchronize()
+    assert torch.equal(inplace, out)

@@ -75,6 +75,8 @@ def _collectives_worker(rank, world):
         if not be.has_multicast:
             return  # no NVSwitch multicast on this machine: the backend fell back (with a warning)
         assert be.ag_transport == "mc" and be.rs_transport == "mc"
+    if os.environ.get("YAFSDP_SYMM_TRANSPORT") == "cp":
+        assert be.ag_transport == "cp" and be.symmetric_gather_output  # the ranks write their shards into the peers' outputs
     torch.manual_seed(rank)
     for shard in (1024, 8 * 1000 * 100 + 8 * 3):
         inp = be.alloc(shard, torch.bfloat16, dev, "gather_input")
@@ -106,7 +108,7 @@ def _collectives_worker(rank, world):
     kernels.check_status()
 
 
-@pytest.mark.parametrize("transport", [None, "sm", "mc"])
+@pytest.mark.parametrize("transport", [None, "sm", "mc", "cp"])
 def test_symm_collectives_match_nccl(transport):
     _run(_collectives_worker, _world(), transport)
 
@@ -137,7 +139,7 @@ def _train_worker(rank, world):
     assert losses["symm"][-1] < losses["symm"][0]
 
 
-@pytest.mark.parametrize("transport", [None, "mc"])
+@pytest.mark.parametrize("transport", [None, "mc", "cp"])
 def test_training_symm_backend_matches_nccl_backend(transport):
     _run(_train_worker, _world(), transport)
 

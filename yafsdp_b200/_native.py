@@ -164,6 +164,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_attn_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _F, _I, _P],
         "yf_gemm_bf16_sumsq": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _F, _I, _P, _P],
+        "yf_gemm_bf16_residual": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _F, _I, _P],
         "yf_gemm_bf16_gathered": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _P, _L, _L, _I, _I, _P, _L, _P],
         "yf_gemm_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _F, _P, _L, _L, _I, _I, _I, _I, _P],
         "yf_gemm_bf16_scatter_grouped": [_I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _P, _P, _L, _I, _I, _I, _I, _P],

@@ -148,6 +148,10 @@ class SymmArena:
         self.offset += nbytes
         return out
 
+    def contains(self, t: torch.Tensor) -> bool:
+        p = t.data_ptr()
+        return any(base <= p < base + nbytes for base, nbytes, _, _ in self.chunks)
+
     def peer_ptrs(self, t: torch.Tensor) -> list[int]:
         p = t.data_ptr()
         for base, nbytes, bases, _ in self.chunks:
@@ -165,6 +169,12 @@ class SymmBackend(CommBackend):
 
     * ``"ce"``: the copy engines (one ``cudaMemcpyAsync`` per peer, spread over a pool of copy streams per collective);
       the all-gather then takes no SM at all, the reduce-scatter only a local sum over staging slots;
+    * ``"cp"`` (all-gather only): the copy engines again, but every rank WRITES its shard into the peers' gather outputs
+      instead of reading theirs.  Copies that one GPU issues as reads of several peers run one after another on one engine
+      (seen in the step trace: seven 50 MB copies back to back, each alone on the links while it runs); writes to different
+      peers can use an engine each.  The gather outputs then live in the shared arena (``symmetric_gather_output=True`` or
+      ``ag_transport="cp"`` at construction) and every gather is bracketed by two device-side barriers on its stream: all
+      ranks are done with what the buffer held / all writes have landed;
     * ``"sm"``: the pull kernels load from peer memory themselves;
     * ``"mc"``: NVSwitch multicast (``multimem``): the switch sums the gradient copies and replicates the parameter
       shards, so each GPU receives 1/world of the gradient bytes and sends each shard once (needs ``multicast=True``).
@@ -194,7 +204,7 @@ class SymmBackend(CommBackend):
 
     def __init__(self, device: torch.device, group: dist.ProcessGroup | None, *, ag_transport: str | None = None,
                  rs_transport: str | None = None, multicast: bool | None = None, ag_ctas: int = 0, rs_ctas: int = 0,
-                 single_comm_stream: bool = False, timeout_ms: int | None = None):
+                 single_comm_stream: bool = False, timeout_ms: int | None = None, symmetric_gather_output: bool = False):
         if group is None or device.type != "cuda":
             raise ValueError("the symmetric backend needs a CUDA device and a process group")
         if group.size() > 16:
@@ -206,12 +216,14 @@ class SymmBackend(CommBackend):
         env = os.environ.get
         both = env("YAFSDP_SYMM_TRANSPORT", "").lower() or None
         ag = (env("YAFSDP_AG_TRANSPORT", "").lower() or both or ag_transport or self.DEFAULT_TRANSPORTS["ag"](self.world)).lower()
-        rs = (env("YAFSDP_RS_TRANSPORT", "").lower() or both or rs_transport or self.DEFAULT_TRANSPORTS["rs"](self.world)).lower()
+        rs = (env("YAFSDP_RS_TRANSPORT", "").lower() or (both if both != "cp" else None) or rs_transport or self.DEFAULT_TRANSPORTS["rs"](self.world)).lower()
         if multicast is None:
             multicast = "mc" in (ag, rs) or env("YAFSDP_SYMM_MULTICAST", "0") == "1"
         self.arena = SymmArena(device, group, chunk_bytes=int(env("YAFSDP_SYMM_CHUNK_MB", "2048")) << 20, multicast=multicast)
         self.pads = self.arena.alloc(self.N_SLOTS * 16 * 8)
         self.has_multicast = bool(self.arena.mc_bases)
+        # gather outputs that peers can write (the push all-gather): decided once, before the groups allocate their buffers
+        self.symmetric_gather_output = symmetric_gather_output or ag == "cp" or env("YAFSDP_SYMM_GATHER_OUTPUT", "0") == "1"
         self._pad_ptrs = _ptr_array(self.arena.peer_ptrs(self.pads))
         self._seq = [0] * self.N_SLOTS
         self.timeout_ms = timeout_ms if timeout_ms is not None else int(env("YAFSDP_SYMM_TIMEOUT_MS", "30000"))
@@ -244,8 +256,11 @@ class SymmBackend(CommBackend):
             if want is None:
                 continue
             want = want.lower()
-            if want not in ("ce", "sm", "mc"):
-                raise ValueError(f"unknown transport {want!r} (expected 'ce', 'sm' or 'mc')")
+            if want not in ("ce", "sm", "mc") and not (kind == "ag" and want == "cp"):
+                raise ValueError(f"unknown transport {want!r} (expected 'ce', 'sm' or 'mc'; 'cp' for the all-gather)")
+            if want == "cp" and not self.symmetric_gather_output:
+                raise ValueError("the push all-gather needs gather outputs in the shared arena: construct the backend with "
+                                 "ag_transport='cp' or symmetric_gather_output=True")
             if want == "mc" and not self.has_multicast:
                 fallback = self.DEFAULT_TRANSPORTS[kind](self.world)
                 if warn and self.rank == 0:
@@ -262,7 +277,7 @@ class SymmBackend(CommBackend):
 
     # ------------------------------------------------------------------ memory
     def alloc(self, numel: int, dtype: torch.dtype, device: torch.device, kind: str) -> torch.Tensor:
-        if kind == "gather_output" and not self.has_multicast:
+        if kind == "gather_output" and not (self.has_multicast or self.symmetric_gather_output):
             return torch.empty(numel, dtype=dtype, device=device)  # only this rank reads or writes it
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         return self.arena.alloc(nbytes)[:nbytes].view(dtype)
@@ -386,7 +401,16 @@ class SymmBackend(CommBackend):
             kernels._check(rc, "yf_allgather_mc")
             self.barrier(self.SLOT_MC_POST)  # every rank's stores have landed in every copy
             return
-        if self.ag_transport == "ce":
+        if self.ag_transport == "cp" and self.arena.contains(out):
+            outs = self._peer_ints(out)
+            src, off = inp.data_ptr(), self.rank * nbytes
+            self.barrier(self.SLOT_MC_PRE)  # every rank is done with what its copy of `out` held before
+            with torch.autograd._unsafe_preserve_version_counter(out):
+                self._ce_copies([(outs[r] + off, src, nbytes) for r in ((self.rank + d) % self.world for d in range(self.world))],
+                                self._ag_ce_streams)
+            self.barrier(self.SLOT_MC_POST)  # every rank's copies have landed in every output
+            return
+        if self.ag_transport in ("ce", "cp"):  # "cp" with an output outside the arena (allocated by the caller): read instead
             peers = self._peer_ints(inp)
             base = out.data_ptr()
             with torch.autograd._unsafe_preserve_version_counter(out):

@@ -211,13 +211,11 @@ class DecoderLayerFn(torch.autograd.Function):
         kernels.rope_(qkv, cos_sin, dims.seq, 0, hq + hkv, hd)
         q, k, v = qkv[:, : hq * hd], qkv[:, hq * hd : (hq + hkv) * hd], qkv[:, (hq + hkv) * hd :]
         att, lse = kernels.attn_fwd(q, k, v, dims.batch, dims.seq, hq, hkv, 1.0 / math.sqrt(hd), True)
-        h = kernels.gemm(att, wo.detach())
-        kernels.add_bf16(x, h, out=h)
+        h = kernels.gemm(att, wo.detach(), residual=x)  # x + attention block: the residual is added in the GEMM's epilogue
         n2, rstd2 = kernels.rmsnorm_fwd(h, w_n2.detach(), dims.eps)
         gu = kernels.gemm(n2, w_gu)
         a = kernels.swiglu_fwd(gu)
-        out = kernels.gemm(a, wd.detach())
-        kernels.add_bf16(h, out, out=out)
+        out = kernels.gemm(a, wd.detach(), residual=h)
         ctx.save_for_backward(x, rstd1, n1, qkv, att, lse, h, rstd2, n2, gu, a, cos_sin)
         ctx.weights = (w_n1, wq, wk, wv, wo, w_n2, wg, wu, wd)
         ctx.dims = dims

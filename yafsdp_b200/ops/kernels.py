@@ -82,13 +82,15 @@ def gemm(
     alpha: float = 1.0,
     sm_limit: int = 0,
     sumsq: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``out[M,N] = alpha * A @ B^T (+ out)`` with bf16 inputs and fp32 accumulation (tcgen05).
 
     ``a`` is ``[M,K]`` (K-major) or, with ``a_mn_major``, the stored tensor is ``[K,M]``; ``b`` is
     ``[N,K]`` or, with ``b_mn_major``, stored ``[K,N]``.  Rows must be contiguous (stride 1 in the last
     dimension); the row pitch may exceed the row length.  ``sumsq`` (fp32 output without accumulation only): a
-    one-element fp32 tensor that receives ``+= sum(out**2)`` from the same kernel.
+    one-element fp32 tensor that receives ``+= sum(out**2)`` from the same kernel.  ``residual`` (bf16 output without
+    accumulation only): a bf16 ``[M,N]`` tensor added in fp32 inside the epilogue, before the output is rounded.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
@@ -105,6 +107,15 @@ def gemm(
         assert not accumulate
         out = torch.empty((m, n), device=a.device, dtype=out_dtype)
     assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if residual is not None:
+        assert out.dtype == torch.bfloat16 and not accumulate and sumsq is None
+        assert residual.dtype == torch.bfloat16 and residual.shape == (m, n) and residual.stride(1) == 1
+        rc = _native.lib().yf_gemm_bf16_residual(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+            residual.stride(0), int(a_mn_major), int(b_mn_major), float(alpha), int(sm_limit), _stream(),
+        )
+        _check(rc, "yf_gemm_bf16_residual")
+        return out
     rc = _native.lib().yf_gemm_bf16_sumsq(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), float(alpha),

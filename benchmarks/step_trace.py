@@ -57,7 +57,7 @@ def summarize(trace_path: str, world: int, steps: int) -> str:
         agg: dict = collections.defaultdict(list)
         for e in es:
             agg[e["name"][:48]].append(e["dur"] / 1e3)
-        for k, v in sorted(agg.items(), key=lambda x: -sum(x[1]))[:8]:
+        for k, v in sorted(agg.items(), key=lambda x: -sum(x[1]))[: 28 if s == main else 8]:
             out.append(f"    {sum(v):8.2f} ms n={len(v):4d} med {statistics.median(v):.3f} max {max(v):.3f}  {k}")
     es = streams[main]
     gaps = []

@@ -160,6 +160,140 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_dx_kernel(const __nv_b
   }
 }
 
+// G warps per row (G = 1, 2 or 4; D <= 32 * G * 8 * RNW_NV), four warps per CTA: the row stays in registers as packed bf16,
+// every operand of a row is requested before anything is reduced (one exposed memory latency per row, not one per pass),
+// and the only synchronisation is a named barrier among the G warps of the row.  Thread t of a row's group holds the
+// vectors t, t + 32 G, ... of the row (contiguous 512 G bytes per load instruction).
+constexpr int RNW_WARPS = 4;
+constexpr int RNW_NV = 8;
+YF_DEVINL void unpack8(const uint4& v, float (&f)[8]) {
+  float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+template <int G>
+YF_DEVINL float row_group_sum(float v, float* red, int row_in_cta) {
+  v = warp_sum(v);
+  if (G == 1) return v;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  if (row_in_cta == 0) named_bar_sync(1, 32 * G);  // literal barrier numbers: a computed one reserves all sixteen
+  else named_bar_sync(2, 32 * G);
+  float t = 0.f;
+#pragma unroll
+  for (int g = 0; g < G; ++g) t += red[row_in_cta * G + g];
+  return t;
+}
+
+template <int G>
+__global__ void __launch_bounds__(RNW_WARPS * 32) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                          const __nv_bfloat16* __restrict__ w,
+                                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                                          int T, int D, float eps) {
+  __shared__ float red[RNW_WARPS];
+  constexpr int ROWS = RNW_WARPS / G, TPR = 32 * G;
+  const int row_in_cta = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int row = blockIdx.x * ROWS + row_in_cta;
+  if (row >= T) return;
+  const int nvec = D / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 xv[RNW_NV], wv[RNW_NV];
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    const int v = tr + TPR * i;
+    xv[i] = v < nvec ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
+    wv[i] = v < nvec ? __ldg(wr + v) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    float f[8];
+    unpack8(xv[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = row_group_sum<G>(ss, red, row_in_cta);
+  const float r = rsqrtf(ss / (float)D + eps);
+  if (tr == 0 && rstd) rstd[row] = r;
+  __nv_bfloat16* yr = y + (size_t)row * D;
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    const int v = tr + TPR * i;
+    if (v < nvec) {
+      float f[8], wf[8], o[8];
+      unpack8(xv[i], f);
+      unpack8(wv[i], wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[j] * r * wf[j];
+      store8(yr + v * 8, o);
+    }
+  }
+}
+
+// dx of the same form; CTA 0 also clears the weight gradient when `dw_zero` is given (the column-reduction kernel that
+// accumulates into it is launched after this one on the same stream).
+template <int G>
+__global__ void __launch_bounds__(RNW_WARPS * 32, 3) rmsnorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                                const __nv_bfloat16* __restrict__ w,
+                                                                                const __nv_bfloat16* __restrict__ dy,
+                                                                                const float* __restrict__ rstd,
+                                                                                const __nv_bfloat16* __restrict__ dres,
+                                                                                __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_zero,
+                                                                                int T, int D) {
+  __shared__ float red[RNW_WARPS];
+  if (dw_zero != nullptr && blockIdx.x == 0)
+    for (int i = threadIdx.x; i < D; i += RNW_WARPS * 32) dw_zero[i] = 0.f;
+  constexpr int ROWS = RNW_WARPS / G, TPR = 32 * G;
+  const int row_in_cta = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int row = blockIdx.x * ROWS + row_in_cta;
+  if (row >= T) return;
+  const int nvec = D / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+  const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
+  const uint4* er = reinterpret_cast<const uint4*>(dres ? dres + (size_t)row * D : x);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 xv[RNW_NV], dv[RNW_NV], ev[RNW_NV];
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    const int v = tr + TPR * i;
+    const bool in = v < nvec;
+    xv[i] = in ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
+    dv[i] = in ? dyr[v] : make_uint4(0u, 0u, 0u, 0u);
+    ev[i] = (in && dres) ? er[v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const float r = rstd[row];
+  // g = dy * w replaces dy in registers (fp32 products rounded to bf16 would lose bits: keep dy and w apart instead and
+  // multiply twice; w comes from L1 both times)
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    const int v = tr + TPR * i;
+    if (v < nvec) {
+      float xf[8], df[8], wf[8];
+      unpack8(xv[i], xf);
+      unpack8(dv[i], df);
+      unpack8(__ldg(wr + v), wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += df[j] * wf[j] * (xf[j] * r);
+    }
+  }
+  dot = row_group_sum<G>(dot, red, row_in_cta) / (float)D;
+  __nv_bfloat16* dxr = dx + (size_t)row * D;
+#pragma unroll
+  for (int i = 0; i < RNW_NV; ++i) {
+    const int v = tr + TPR * i;
+    if (v < nvec) {
+      float xf[8], df[8], wf[8], ef[8], o[8];
+      unpack8(xv[i], xf);
+      unpack8(dv[i], df);
+      unpack8(ev[i], ef);
+      unpack8(__ldg(wr + v), wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = r * (df[j] * wf[j] - xf[j] * r * dot) + ef[j];
+      store8(dxr + v * 8, o);
+    }
+  }
+}
+
 constexpr int RN_DW_COLS = 64;     // columns per CTA (8 threads x 8 bf16)
 constexpr int RN_DW_ROWLANES = 32; // row lanes per CTA (256 threads / 8)
 __global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
@@ -509,19 +643,43 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 extern "C" int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream) {
   if (T <= 0 || D <= 0 || (D % 8) || !aligned16(x) || !aligned16(w) || !aligned16(y)) return -1;
+  if (D <= 32 * 4 * 8 * RNW_NV) {  // G warps per row
+    const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w;
+    __nv_bfloat16* yp = (__nv_bfloat16*)y;
+    const int g = D <= 32 * 8 * RNW_NV ? 1 : (D <= 64 * 8 * RNW_NV ? 2 : 4);
+    const int rows = RNW_WARPS / g, ctas = (T + rows - 1) / rows;
+    if (g == 1) rmsnorm_fwd_warp_kernel<1><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, yp, rstd, T, D, eps);
+    else if (g == 2) rmsnorm_fwd_warp_kernel<2><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, yp, rstd, T, D, eps);
+    else rmsnorm_fwd_warp_kernel<4><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, yp, rstd, T, D, eps);
+    YF_LAUNCH_RET();
+  }
   const int grid = T < yf_num_sms() * 8 ? T : yf_num_sms() * 8;
   rmsnorm_fwd_kernel<<<grid, RN_THREADS, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                                                  (__nv_bfloat16*)y, rstd, T, D, eps);
   YF_LAUNCH_RET();
 }
 extern "C" int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
-                              float* dw, int T, int D, void* stream) {
+                              float* dw, int zero_dw, int T, int D, void* stream) {
   if (T <= 0 || D <= 0 || (D % 8) || D > RN_THREADS * 8 * RN_MAXV) return -1;
   if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dx) || (dres && !aligned16(dres))) return -1;
-  const int grid = T < yf_num_sms() * 8 ? T : yf_num_sms() * 8;
-  rmsnorm_bwd_dx_kernel<<<grid, RN_THREADS, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                                    (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
-                                                                    (__nv_bfloat16*)dx, T, D);
+  if (zero_dw && !dw) return -1;
+  if (D <= 32 * 4 * 8 * RNW_NV) {  // G warps per row
+    const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w, *dyp = (const __nv_bfloat16*)dy,
+                        *ep = (const __nv_bfloat16*)dres;
+    __nv_bfloat16* dxp = (__nv_bfloat16*)dx;
+    float* dwz = zero_dw ? dw : nullptr;
+    const int g = D <= 32 * 8 * RNW_NV ? 1 : (D <= 64 * 8 * RNW_NV ? 2 : 4);
+    const int rows = RNW_WARPS / g, ctas = (T + rows - 1) / rows;
+    if (g == 1) rmsnorm_bwd_dx_warp_kernel<1><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, dyp, rstd, ep, dxp, dwz, T, D);
+    else if (g == 2) rmsnorm_bwd_dx_warp_kernel<2><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, dyp, rstd, ep, dxp, dwz, T, D);
+    else rmsnorm_bwd_dx_warp_kernel<4><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, dyp, rstd, ep, dxp, dwz, T, D);
+  } else {
+    if (zero_dw && cudaMemsetAsync(dw, 0, (size_t)D * sizeof(float), YF_STREAM(stream)) != cudaSuccess) return -2;
+    const int grid = T < yf_num_sms() * 8 ? T : yf_num_sms() * 8;
+    rmsnorm_bwd_dx_kernel<<<grid, RN_THREADS, 0, YF_STREAM(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                                      (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
+                                                                      (__nv_bfloat16*)dx, T, D);
+  }
   if (dw) {
     const int col_blocks = (D + RN_DW_COLS - 1) / RN_DW_COLS;
     int splits = (yf_num_sms() * 6 + col_blocks - 1) / col_blocks;  // about six CTAs per SM in total

@@ -41,8 +41,9 @@ int yf_gemm_bf16_scatter_grouped(int n, const void* const* A, const void* const*
 
 // ---- memory-bound kernels (elementwise.cu)
 int yf_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, void* stream);
+/* dx (+ dres) and dw += column sums of dy * xhat; zero_dw: dw is cleared first, inside the dx kernel (no fill launch) */
 int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
-                   float* dw, int T, int D, void* stream);
+                   float* dw, int zero_dw, int T, int D, void* stream);
 int yf_rope(void* qkv, const float* cos_sin, int T, int seq_len, long long row_stride, int col0, int n_heads,
             int head_dim, int backward, void* stream);
 int yf_swiglu_fwd(const void* gu, void* h, long long T, int F, void* stream);

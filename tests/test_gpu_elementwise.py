@@ -12,7 +12,7 @@ def _close(a, b, rtol=2e-2, atol=2e-2):
     assert torch.allclose(a.float(), b.float(), rtol=rtol, atol=atol), (a.float() - b.float()).abs().max().item()
 
 
-@pytest.mark.parametrize("t,d", [(64, 256), (300, 4096), (17, 8192), (33, 1000 * 8)])
+@pytest.mark.parametrize("t,d", [(64, 256), (300, 4096), (17, 8192), (33, 1000 * 8), (2049, 2048), (130, 5120), (5, 2056)])
 def test_rmsnorm_fwd_bwd(t, d):
     from yafsdp_b200.ops import kernels
 
@@ -31,6 +31,11 @@ def test_rmsnorm_fwd_bwd(t, d):
     dx = kernels.rmsnorm_bwd(x, w, dy, rstd, dw, dres)
     _close(dx, xf.grad + dres.float(), rtol=3e-2, atol=3e-2)
     assert torch.allclose(dw, wf.grad, rtol=2e-2, atol=5e-2 * math.sqrt(t))
+    # without the residual gradient, and with the weight gradient cleared by the kernel itself
+    dw2 = torch.full((d,), 7.0, device="cuda", dtype=torch.float32)
+    dx2 = kernels.rmsnorm_bwd(x, w, dy, rstd, dw2, zero_dw=True)
+    _close(dx2, xf.grad, rtol=3e-2, atol=3e-2)
+    assert torch.allclose(dw2, wf.grad, rtol=2e-2, atol=5e-2 * math.sqrt(t))
 
 
 def test_rope_roundtrip_and_reference():

@@ -147,7 +147,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_status_read": [_P, _P, _I],
         "yf_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _F, _I, _P],
         "yf_rmsnorm_fwd": [_P, _P, _P, _P, _I, _I, _F, _P],
-        "yf_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "yf_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
         "yf_rope": [_P, _P, _I, _I, _L, _I, _I, _I, _I, _P],
         "yf_swiglu_fwd": [_P, _P, _L, _I, _P],
         "yf_swiglu_bwd": [_P, _P, _P, _L, _I, _P],

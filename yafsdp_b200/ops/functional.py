@@ -136,26 +136,35 @@ def flush_pushed(deferred: "list[tuple[Any, ...]]") -> None:
     deferred.clear()
 
 
-def _norm_weight_grad(w: torch.Tensor, fn: Any) -> torch.Tensor | None:
-    """Run ``fn(dw_fp32)`` (a kernel that atomically accumulates into dw); returns the gradient unless sunk."""
+def _norm_weight_grad(w: torch.Tensor, fn: Any, self_zeroing: bool = False) -> torch.Tensor | None:
+    """Run ``fn(dw_fp32)`` (a kernel that atomically accumulates into dw); returns the gradient unless sunk.
+    ``self_zeroing``: the kernel can clear its target itself and is called as ``fn(dw, zero)``."""
     s = _sink(w)
     if s is not None and s.pushes():
-        dw = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
-        fn(dw)
+        dw = torch.empty(w.shape, device=w.device, dtype=torch.float32) if self_zeroing else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        fn(dw, True) if self_zeroing else fn(dw)
         s.push_from(dw)
         return None
     if s is not None and s.local_ok:
         zeroed_now = not s.would_accumulate()
-        view, _ = s.begin(zero=True)
-        fn(view)
+        if self_zeroing:
+            view, _ = s.begin(zero=False)
+            fn(view, zeroed_now)
+        else:
+            view, _ = s.begin(zero=True)
+            fn(view)
         # the value is final (and its squares may be summed here) only if this call started from zeros: an earlier write
         # of this backward pass or an earlier micro-batch's gradient makes it a partial sum
         tgt = s.norm_target(not zeroed_now)
         if tgt is not None:
             kernels.sumsq_(view.reshape(-1), tgt)
         return None
-    dw = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
-    fn(dw)
+    if self_zeroing:
+        dw = torch.empty(w.shape, device=w.device, dtype=torch.float32)
+        fn(dw, True)
+    else:
+        dw = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        fn(dw)
     return dw.to(w.dtype)
 
 
@@ -241,7 +250,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_wg, g_wu = _WeightGrad([wg, wu]).run(dgu, n2, pushed)
         del dgu
         box: list[torch.Tensor] = []
-        g_n2 = _norm_weight_grad(w_n2, lambda dw: box.append(kernels.rmsnorm_bwd(h, w_n2.detach(), dn2, rstd2, dw, dres=dout)))
+        g_n2 = _norm_weight_grad(w_n2, lambda dw, z: box.append(kernels.rmsnorm_bwd(h, w_n2.detach(), dn2, rstd2, dw, dres=dout, zero_dw=z)), True)
         dh = box.pop()
         # ---- attention
         datt = kernels.gemm(dh, wo.detach(), b_mn_major=True)
@@ -253,7 +262,7 @@ class DecoderLayerFn(torch.autograd.Function):
         kernels.rope_(dqkv, cos_sin, dims.seq, 0, hq + hkv, hd, backward=True)
         dn1 = kernels.gemm(dqkv, w_qkv, b_mn_major=True)
         g_wq, g_wk, g_wv = _WeightGrad([wq, wk, wv]).run(dqkv, n1, pushed)
-        g_n1 = _norm_weight_grad(w_n1, lambda dw: box.append(kernels.rmsnorm_bwd(x, w_n1.detach(), dn1, rstd1, dw, dres=dh)))
+        g_n1 = _norm_weight_grad(w_n1, lambda dw, z: box.append(kernels.rmsnorm_bwd(x, w_n1.detach(), dn1, rstd1, dw, dres=dh, zero_dw=z)), True)
         dx = box.pop()
         flush_pushed(pushed)
         return dx, g_n1, g_wq, g_wk, g_wv, g_wo, g_n2, g_wg, g_wu, g_wd, None, None
@@ -283,7 +292,7 @@ class HeadLossFn(torch.autograd.Function):
         dn = kernels.gemm(dlogits, w_head.detach(), b_mn_major=True)
         (g_head,) = _WeightGrad([w_head]).run(dlogits, n)
         box: list[torch.Tensor] = []
-        g_norm = _norm_weight_grad(w_norm, lambda dw: box.append(kernels.rmsnorm_bwd(h, w_norm.detach(), dn, rstd, dw)))
+        g_norm = _norm_weight_grad(w_norm, lambda dw, z: box.append(kernels.rmsnorm_bwd(h, w_norm.detach(), dn, rstd, dw, zero_dw=z)), True)
         return box.pop(), g_norm, g_head, None, None
 
 
@@ -306,7 +315,7 @@ class HeadLogitsFn(torch.autograd.Function):
         dn = kernels.gemm(dlogits, w_head.detach(), b_mn_major=True)
         (g_head,) = _WeightGrad([w_head]).run(dlogits, n)
         box: list[torch.Tensor] = []
-        g_norm = _norm_weight_grad(w_norm, lambda dw: box.append(kernels.rmsnorm_bwd(h, w_norm.detach(), dn, rstd, dw)))
+        g_norm = _norm_weight_grad(w_norm, lambda dw, z: box.append(kernels.rmsnorm_bwd(h, w_norm.detach(), dn, rstd, dw, zero_dw=z)), True)
         return box.pop(), g_norm, g_head, None
 
 

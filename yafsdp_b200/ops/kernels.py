@@ -200,13 +200,14 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float) -> tuple[torch.Ten
 
 
 def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, rstd: torch.Tensor, dw_f32: torch.Tensor,
-                dres: torch.Tensor | None = None) -> torch.Tensor:
-    """Returns dx (+ dres when given); accumulates the weight gradient into the fp32 tensor ``dw_f32``."""
+                dres: torch.Tensor | None = None, zero_dw: bool = False) -> torch.Tensor:
+    """Returns dx (+ dres when given); accumulates the weight gradient into the fp32 tensor ``dw_f32`` (``zero_dw``: the
+    kernel clears it first, which saves the caller a fill launch)."""
     t, d = x.shape
     dx = torch.empty_like(x)
     assert dw_f32.dtype == torch.float32 and dw_f32.numel() == d
     _check(_native.lib().yf_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), _ptr(dres), dx.data_ptr(),
-                                        dw_f32.data_ptr(), t, d, _stream()), "yf_rmsnorm_bwd")
+                                        dw_f32.data_ptr(), int(zero_dw), t, d, _stream()), "yf_rmsnorm_bwd")
     return dx
 
 

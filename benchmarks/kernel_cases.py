@@ -6,7 +6,9 @@ Cases hold a few hundred MB on the device (inputs larger than the 126 MB L2, far
 ncu capture short) and launch the kernel a handful of times.  Each prints the CUDA-event time of one launch and the
 achieved fraction of the measured peak (``MEASURED_PEAKS.json``: copy bandwidth / cuBLAS bf16 throughput).
 
-Cases: gemm_fwd, gemm_dx, gemm_dw, attn_fwd, attn_bwd, adamw, rmsnorm, swiglu, cross_entropy
+Cases: gemm_fwd, gemm_dx, gemm_dw, attn_fwd, attn_bwd, adamw, rmsnorm, swiglu, cross_entropy, and the memory-bound kernels at
+the size they have inside a Llama-2-7B step (2048 tokens), cycling through enough copies of their operands that no launch
+finds them in the L2: step_rmsnorm_fwd, step_rmsnorm_bwd, step_swiglu_fwd, step_swiglu_bwd, step_rope.  ``all_step`` runs those five.
 """
 
 from __future__ import annotations
@@ -49,6 +51,53 @@ def run(fn, iters: int) -> float:
     return s.elapsed_time(e) / iters
 
 
+def step_case(name: str, iters: int, hbm: float) -> dict:
+    """One memory-bound kernel at its in-step size; operands rotate through ``copies`` buffers (> 2 x L2 in total)."""
+    dev, bf = "cuda", torch.bfloat16
+    t, d, f, hq = 2048, 4096, 11008, 32
+    from yafsdp_b200.ops.functional import rope_table
+
+    if name == "step_rmsnorm_fwd":
+        nbytes = 2 * 2.0 * t * d
+        mk = lambda: (torch.randn(t, d, device=dev, dtype=bf),)
+        w = torch.ones(d, device=dev, dtype=bf)
+        call = lambda x: kernels.rmsnorm_fwd(x, w, 1e-5)
+    elif name == "step_rmsnorm_bwd":
+        nbytes = 4 * 2.0 * t * d
+        w = torch.ones(d, device=dev, dtype=bf)
+        dw = torch.zeros(d, device=dev, dtype=torch.float32)
+        rstd = torch.ones(t, device=dev, dtype=torch.float32)
+        mk = lambda: tuple(torch.randn(t, d, device=dev, dtype=bf) for _ in range(3))
+        call = lambda x, dy, dres: kernels.rmsnorm_bwd(x, w, dy, rstd, dw, dres=dres, zero_dw=True)
+    elif name == "step_swiglu_fwd":
+        nbytes = 3 * 2.0 * t * f
+        mk = lambda: (torch.randn(t, 2 * f, device=dev, dtype=bf),)
+        call = lambda gu: kernels.swiglu_fwd(gu)
+    elif name == "step_swiglu_bwd":
+        nbytes = 5 * 2.0 * t * f
+        mk = lambda: (torch.randn(t, 2 * f, device=dev, dtype=bf), torch.randn(t, f, device=dev, dtype=bf))
+        call = lambda gu, da: kernels.swiglu_bwd(gu, da)
+    elif name == "step_rope":
+        nbytes = 2 * 2.0 * t * 2 * hq * 128
+        cs = rope_table(t, 128, 10000.0, torch.device(dev))
+        mk = lambda: (torch.randn(t, 3 * hq * 128, device=dev, dtype=bf),)
+        call = lambda qkv: kernels.rope_(qkv, cs, t, 0, 2 * hq, 128)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    copies = max(2, int(300e6 // nbytes) + 1)
+    bufs = [mk() for _ in range(copies)]
+    for b in bufs:  # warm-up (also outside the graph: first-use initialisation must not be captured)
+        call(*b)
+    torch.cuda.synchronize()
+    # one CUDA graph of a launch per copy: the kernels run back to back, without the host's launch cost between them
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for b in bufs:
+            call(*b)
+    ms = run(graph.replay, max(iters, 5)) / copies
+    return {"case": name, "us": round(ms * 1e3, 2), "gbs": round(nbytes / ms / 1e6, 1), "fraction_of_measured_hbm_peak": round(nbytes / ms / 1e6 / hbm, 3)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
@@ -59,6 +108,13 @@ def main() -> None:
     t, d, f = 2048, 4096, 11008
     bf = torch.bfloat16
     flops = bytes_ = 0.0
+    if a.case == "all_step" or a.case.startswith("step_"):
+        names = ["step_rmsnorm_fwd", "step_rmsnorm_bwd", "step_swiglu_fwd", "step_swiglu_bwd", "step_rope"] if a.case == "all_step" else [a.case]
+        for n in names:
+            rec = step_case(n, a.iters, hbm)
+            rec["status"] = list(kernels.status())
+            print(json.dumps(rec))
+        return
     if a.case == "gemm_fwd":  # gate/up projection: [T,d] x [2f,d]^T
         x, w = torch.randn(t, d, device=dev, dtype=bf), torch.randn(2 * f, d, device=dev, dtype=bf)
         out = torch.empty(t, 2 * f, device=dev, dtype=bf)

@@ -160,12 +160,13 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_dx_kernel(const __nv_b
   }
 }
 
-// G warps per row (G = 1, 2 or 4; D <= 32 * G * 8 * RNW_NV), four warps per CTA: the row stays in registers as packed bf16,
+// G warps per row (G = 1, 2 or 4; D <= 32 * G * 8 * RNW_NV forward, RNW_NV_B backward), four warps per CTA: the row stays in registers as packed bf16,
 // every operand of a row is requested before anything is reduced (one exposed memory latency per row, not one per pass),
 // and the only synchronisation is a named barrier among the G warps of the row.  Thread t of a row's group holds the
 // vectors t, t + 32 G, ... of the row (contiguous 512 G bytes per load instruction).
 constexpr int RNW_WARPS = 4;
-constexpr int RNW_NV = 8;
+constexpr int RNW_NV = 8;    // forward: vectors of a row per thread
+constexpr int RNW_NV_B = 4;  // backward (three operands per row in registers)
 YF_DEVINL void unpack8(const uint4& v, float (&f)[8]) {
   float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(RNW_WARPS * 32) rmsnorm_fwd_warp_kernel(const 
 // dx of the same form; CTA 0 also clears the weight gradient when `dw_zero` is given (the column-reduction kernel that
 // accumulates into it is launched after this one on the same stream).
 template <int G>
-__global__ void __launch_bounds__(RNW_WARPS * 32, 3) rmsnorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(RNW_WARPS * 32, 6) rmsnorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                 const __nv_bfloat16* __restrict__ w,
                                                                                 const __nv_bfloat16* __restrict__ dy,
                                                                                 const float* __restrict__ rstd,
@@ -251,9 +252,9 @@ __global__ void __launch_bounds__(RNW_WARPS * 32, 3) rmsnorm_bwd_dx_warp_kernel(
   const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
   const uint4* er = reinterpret_cast<const uint4*>(dres ? dres + (size_t)row * D : x);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  uint4 xv[RNW_NV], dv[RNW_NV], ev[RNW_NV];
+  uint4 xv[RNW_NV_B], dv[RNW_NV_B], ev[RNW_NV_B];
 #pragma unroll
-  for (int i = 0; i < RNW_NV; ++i) {
+  for (int i = 0; i < RNW_NV_B; ++i) {
     const int v = tr + TPR * i;
     const bool in = v < nvec;
     xv[i] = in ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__(RNW_WARPS * 32, 3) rmsnorm_bwd_dx_warp_kernel(
   // multiply twice; w comes from L1 both times)
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < RNW_NV; ++i) {
+  for (int i = 0; i < RNW_NV_B; ++i) {
     const int v = tr + TPR * i;
     if (v < nvec) {
       float xf[8], df[8], wf[8];
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(RNW_WARPS * 32, 3) rmsnorm_bwd_dx_warp_kernel(
   dot = row_group_sum<G>(dot, red, row_in_cta) / (float)D;
   __nv_bfloat16* dxr = dx + (size_t)row * D;
 #pragma unroll
-  for (int i = 0; i < RNW_NV; ++i) {
+  for (int i = 0; i < RNW_NV_B; ++i) {
     const int v = tr + TPR * i;
     if (v < nvec) {
       float xf[8], df[8], wf[8], ef[8], o[8];
@@ -663,12 +664,12 @@ extern "C" int yf_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
   if (T <= 0 || D <= 0 || (D % 8) || D > RN_THREADS * 8 * RN_MAXV) return -1;
   if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dx) || (dres && !aligned16(dres))) return -1;
   if (zero_dw && !dw) return -1;
-  if (D <= 32 * 4 * 8 * RNW_NV) {  // G warps per row
+  if (D <= 32 * 4 * 8 * RNW_NV_B) {  // G warps per row
     const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w, *dyp = (const __nv_bfloat16*)dy,
                         *ep = (const __nv_bfloat16*)dres;
     __nv_bfloat16* dxp = (__nv_bfloat16*)dx;
     float* dwz = zero_dw ? dw : nullptr;
-    const int g = D <= 32 * 8 * RNW_NV ? 1 : (D <= 64 * 8 * RNW_NV ? 2 : 4);
+    const int g = D <= 32 * 8 * RNW_NV_B ? 1 : (D <= 64 * 8 * RNW_NV_B ? 2 : 4);
     const int rows = RNW_WARPS / g, ctas = (T + rows - 1) / rows;
     if (g == 1) rmsnorm_bwd_dx_warp_kernel<1><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, dyp, rstd, ep, dxp, dwz, T, D);
     else if (g == 2) rmsnorm_bwd_dx_warp_kernel<2><<<ctas, RNW_WARPS * 32, 0, YF_STREAM(stream)>>>(xp, wp, dyp, rstd, ep, dxp, dwz, T, D);

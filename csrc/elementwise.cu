@@ -401,15 +401,18 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 }
 
 // ------------------------------------------------------------------ cross-entropy (forward + backward in one pass pair)
-// logits [T, V] bf16 (row pitch ldl) are replaced in place by dlogits = (softmax - onehot) * grad_scale;
+// logits [T, V] bf16 (row pitch ldl) are replaced in place by dlogits = (softmax - onehot) * grad_scale, where grad_scale is
+// the host value times *scale_ptr when that device pointer is given (e.g. 1 / number of valid labels, counted on the device);
 // loss_rows[t] = logsumexp - logit[label] (0 for ignored rows, label < 0).  One CTA per row.
 constexpr int CE_THREADS = 512;
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
                                                                    const long long* __restrict__ labels,
                                                                    float* __restrict__ loss_rows, int T, int V,
-                                                                   long long ldl, float grad_scale, int write_grad) {
+                                                                   long long ldl, float grad_scale,
+                                                                   const float* __restrict__ scale_ptr, int write_grad) {
   __shared__ float red[32];
   const int nvec = V / 8;
+  if (scale_ptr != nullptr) grad_scale *= *scale_ptr;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     __nv_bfloat16* lr = logits + (size_t)row * ldl;
     const long long label = labels[row];
@@ -714,11 +717,11 @@ extern "C" int yf_swiglu_bwd(const void* gu, const void* dh, void* dgu, long lon
   YF_LAUNCH_RET();
 }
 extern "C" int yf_cross_entropy(void* logits, const long long* labels, float* loss_rows, int T, int V, long long ldl,
-                                float grad_scale, int write_grad, void* stream) {
+                                float grad_scale, const float* scale_ptr, int write_grad, void* stream) {
   if (T <= 0 || V <= 0 || (ldl % 8) || !aligned16(logits)) return -1;
   const int grid = T < yf_num_sms() * 4 ? T : yf_num_sms() * 4;
   cross_entropy_kernel<<<grid, CE_THREADS, 0, YF_STREAM(stream)>>>((__nv_bfloat16*)logits, labels, loss_rows, T, V, ldl, grad_scale,
-                                                                   write_grad);
+                                                                   scale_ptr, write_grad);
   YF_LAUNCH_RET();
 }
 extern "C" int yf_embedding_fwd(const void* table, const long long* ids, void* out, long long T, int D, int V, void* stream) {

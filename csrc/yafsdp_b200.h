@@ -49,7 +49,7 @@ int yf_rope(void* qkv, const float* cos_sin, int T, int seq_len, long long row_s
 int yf_swiglu_fwd(const void* gu, void* h, long long T, int F, void* stream);
 int yf_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long T, int F, void* stream);
 int yf_cross_entropy(void* logits, const long long* labels, float* loss_rows, int T, int V, long long ldl,
-                     float grad_scale, int write_grad, void* stream);
+                     float grad_scale, const float* scale_ptr, int write_grad, void* stream);
 int yf_embedding_fwd(const void* table, const long long* ids, void* out, long long T, int D, int V, void* stream);
 int yf_embedding_bwd(const void* dout, const long long* ids, float* dtable, long long T, int D, int V, void* stream);
 int yf_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, const float* grad_scale_ptr, long long n,

@@ -93,6 +93,13 @@ def test_cross_entropy(v):
     loss_rows = kernels.cross_entropy_(logits, labels, 1.0)
     assert abs(loss_rows.sum().item() - ref.item()) <= 2e-3 * abs(ref.item()) + 1e-2
     assert torch.allclose(logits.float(), lf.grad, rtol=2e-2, atol=4e-3)
+    # the gradient scale as host value x device scalar (what the mean over valid labels uses)
+    buf2 = torch.zeros_like(buf)
+    logits2 = buf2[:, :v]
+    logits2.copy_(lf.detach())
+    dev_scale = torch.tensor([0.25], device="cuda")
+    kernels.cross_entropy_(logits2, labels, 0.5, scale=dev_scale)
+    assert torch.allclose(logits2.float(), lf.grad * 0.125, rtol=2e-2, atol=1e-3)
 
 
 def test_embedding():

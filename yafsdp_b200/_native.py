@@ -151,7 +151,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "yf_rope": [_P, _P, _I, _I, _L, _I, _I, _I, _I, _P],
         "yf_swiglu_fwd": [_P, _P, _L, _I, _P],
         "yf_swiglu_bwd": [_P, _P, _P, _L, _I, _P],
-        "yf_cross_entropy": [_P, _P, _P, _I, _I, _L, _F, _I, _P],
+        "yf_cross_entropy": [_P, _P, _P, _I, _I, _L, _F, _P, _I, _P],
         "yf_embedding_fwd": [_P, _P, _P, _L, _I, _I, _P],
         "yf_embedding_bwd": [_P, _P, _P, _L, _I, _I, _P],
         "yf_adamw": [_P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _I, _P],

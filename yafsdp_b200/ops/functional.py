@@ -278,19 +278,22 @@ class HeadLossFn(torch.autograd.Function):
         h = _c(h)
         n, rstd = kernels.rmsnorm_fwd(h, w_norm.detach(), eps)
         logits = kernels.gemm(n, w_head.detach())
-        loss_rows = kernels.cross_entropy_(logits, labels, 1.0, write_grad=True)
-        n_valid = (labels >= 0).sum().clamp_(min=1).to(torch.float32)
-        ctx.save_for_backward(h, rstd, n, logits, n_valid)
+        # the mean's 1 / (number of valid labels) goes into the gradient that the loss kernel leaves in place of the logits
+        inv_valid = (labels >= 0).sum().clamp_(min=1).to(torch.float32).reciprocal_().reshape(1)
+        loss_rows = kernels.cross_entropy_(logits, labels, 1.0, write_grad=True, scale=inv_valid)
+        ctx.save_for_backward(h, rstd, n, logits)
         ctx.weights = (w_norm, w_head)
-        return loss_rows.sum() / n_valid
+        return (loss_rows.sum() * inv_valid).reshape(())
 
     @staticmethod
     def backward(ctx: Any, dloss: torch.Tensor) -> Any:  # type: ignore[override]
-        h, rstd, n, dlogits, n_valid = ctx.saved_tensors
+        h, rstd, n, dlogits = ctx.saved_tensors
         w_norm, w_head = ctx.weights
-        dlogits.mul_((dloss / n_valid).to(dlogits.dtype))
+        # the incoming gradient of the loss (a device scalar) scales the two small [T, d] operands instead of a pass over
+        # the [T, vocab] gradient: dn = dloss * (dlogits W), dW = dlogits^T (dloss * n)
         dn = kernels.gemm(dlogits, w_head.detach(), b_mn_major=True)
-        (g_head,) = _WeightGrad([w_head]).run(dlogits, n)
+        dn.mul_(dloss.to(dn.dtype))
+        (g_head,) = _WeightGrad([w_head]).run(dlogits, n * dloss.to(n.dtype))
         box: list[torch.Tensor] = []
         g_norm = _norm_weight_grad(w_norm, lambda dw, z: box.append(kernels.rmsnorm_bwd(h, w_norm.detach(), dn, rstd, dw, zero_dw=z)), True)
         return box.pop(), g_norm, g_head, None, None

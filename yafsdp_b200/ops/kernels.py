@@ -235,13 +235,15 @@ def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
     return dgu
 
 
-def cross_entropy_(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float, write_grad: bool = True) -> torch.Tensor:
-    """Per-row losses; ``logits`` is overwritten by ``(softmax - onehot) * grad_scale`` when ``write_grad``."""
+def cross_entropy_(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float, write_grad: bool = True,
+                   scale: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-row losses; ``logits`` is overwritten by ``(softmax - onehot) * grad_scale`` when ``write_grad``.  ``scale``: a
+    one-element fp32 device tensor whose value multiplies ``grad_scale`` (read by the kernel: no host synchronisation)."""
     t, v = logits.shape
     assert labels.dtype == torch.int64 and logits.stride(1) == 1
     loss_rows = torch.empty(t, device=logits.device, dtype=torch.float32)
     _check(_native.lib().yf_cross_entropy(logits.data_ptr(), labels.data_ptr(), loss_rows.data_ptr(), t, v, logits.stride(0),
-                                          float(grad_scale), int(write_grad), _stream()), "yf_cross_entropy")
+                                          float(grad_scale), _ptr(scale), int(write_grad), _stream()), "yf_cross_entropy")
     return loss_rows
 
 

@@ -284,21 +284,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   }
 }
 
-// delta[b,h,s] = sum_d dO * O ; one warp per (token, head)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                  float* __restrict__ delta, int B, int S, int Hq, long long o_stride, long long do_stride) {
+// delta[b,h,s] = sum_d dO * O, and the fp32 dQ accumulator of the same (token, head) cleared on the way (the main kernel
+// adds into it): sixteen lanes per (token, head), one 16-byte load of O and of dO and two 16-byte stores of zeros per lane.
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                         float* __restrict__ delta, float* __restrict__ dq_zero, int B, int S, int Hq,
+                                                         long long o_stride, long long do_stride) {
   const long long total = (long long)B * S * Hq;
-  const int lane = threadIdx.x & 31;
-  for (long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((long long)gridDim.x * blockDim.x) >> 5) {
+  const int sub = threadIdx.x & 15;
+  const unsigned half_mask = 0xffffu << (threadIdx.x & 16);  // the two halves of a warp may leave the loop at different times
+  for (long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 4; w < total;
+       w += ((long long)gridDim.x * blockDim.x) >> 4) {
     const int h = (int)(w % Hq);
     const long long t = w / Hq;
-    const uint2 a = *reinterpret_cast<const uint2*>(o + t * o_stride + h * HD + lane * 4);
-    const uint2 g = *reinterpret_cast<const uint2*>(d_o + t * do_stride + h * HD + lane * 4);
-    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
-    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
-    s = warp_sum(s);
-    if (lane == 0) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + t * o_stride + h * HD + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + t * do_stride + h * HD + sub * 8);
+    if (dq_zero != nullptr) {
+      float4* z = reinterpret_cast<float4*>(dq_zero + (t * Hq + h) * HD + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y + a3.x * g3.x + a3.y * g3.y;
+#pragma unroll
+    for (int m = 8; m >= 1; m >>= 1) s += __shfl_xor_sync(half_mask, s, m);
+    if (sub == 0) {
       const long long bb = t / S, ss = t % S;
       delta[(bb * Hq + h) * S + ss] = s;
     }
@@ -343,15 +353,15 @@ static int attn_bwd_launch(const CUtensorMap& mq, const CUtensorMap& mk, const C
   }
   if (int rc = yf_tu_bind_status()) return rc;
   const long long T = (long long)B * S;
-  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * HD * sizeof(float), st);  // must start at zero on every call
-  if (e != cudaSuccess) return -(int)e;
   {
-    const long long warps = T * Hq;
-    long long blocks = (warps * 32 + 255) / 256;
+    // delta pre-pass; it also clears the dQ accumulator, which must start at zero on every call
+    const long long groups = T * Hq;
+    long long blocks = (groups * 16 + 255) / 256;
     const long long cap = (long long)yf_num_sms() * 8;
     if (blocks > cap) blocks = cap;
     attn_delta_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
-                                                  reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq, o_stride, do_stride);
+                                                  reinterpret_cast<const __nv_bfloat16*>(dout), delta, dq_accum, B, S, Hq, o_stride,
+                                                  do_stride);
   }
   BwdArgs a;
   a.lse = lse;

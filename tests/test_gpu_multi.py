@@ -1,8 +1,10 @@
 """Multi-GPU checks (skipped with fewer than 2 GPUs): peer-memory collectives vs NCCL, and sharded training with
 the peer-memory backend vs the NCCL backend."""
 
+import datetime
 import os
 import socket
+import time
 import traceback
 
 import pytest
@@ -22,10 +24,13 @@ def _entry(rank, world, port, fn, errq, transport=None):
 
     if transport:
         os.environ["YAFSDP_SYMM_TRANSPORT"] = transport
+    # a rank that fails must not leave its peers waiting for minutes: short limits on device-side waits and on NCCL
+    os.environ.setdefault("YAFSDP_SYMM_TIMEOUT_MS", "20000")
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
     try:
         torch.cuda.set_device(rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=120))
         fn(rank, world)
         torch.cuda.synchronize()
     except Exception:
@@ -45,8 +50,9 @@ def _run(fn, world, transport=None):
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, errq, transport)) for r in range(world)]
     for p in procs:
         p.start()
+    deadline = time.monotonic() + 240  # for all ranks together: the tiny models below need well under a minute
     for p in procs:
-        p.join(300)
+        p.join(max(1.0, deadline - time.monotonic()))
     alive = [p for p in procs if p.is_alive()]
     for p in alive:
         p.kill()

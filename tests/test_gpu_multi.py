@@ -253,7 +253,7 @@ def _unshard_after_step_worker(rank, world):
 
     dev = torch.device("cuda", rank)
     cfg = CONFIGS["tiny-gpu"]
-    model = build_llama(cfg, dev, comm_backend="symm")
+    model = build_llama(cfg, dev, comm_backend="symm", fused_reduce=False)  # the plain reduce-scatter: this test is about gathers
     opt = torch.optim.AdamW(model.parameters(), lr=1e-2)  # a stock optimizer: the gather inputs go stale after its step
     ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
     for _ in range(2):
@@ -340,7 +340,7 @@ def _hpz_worker(rank, world):
     mine = groups[rank // n]
     losses = {}
     for hpz in (False, True):
-        model = build_llama(cfg, dev, comm_backend="symm")
+        model = build_llama(cfg, dev, comm_backend="symm", fused_reduce=False)
         if hpz:
             for layer in model.model.layers:
                 layer.set_secondary_shard_group(mine)

@@ -153,7 +153,7 @@ def test_training_symm_backend_matches_nccl_backend(transport):
 def _fused_worker(rank, world):
     """All-gather -> GEMM and GEMM -> reduce-scatter fused kernels against NCCL + the plain GEMM."""
     import torch.distributed as dist
-    from yafsdp_b200.comm.symm import SymmBackend, _ptr_array
+    from yafsdp_b200.comm.symm import SymmBackend
     from yafsdp_b200.ops import kernels
 
     dev = torch.device("cuda", rank)

@@ -130,7 +130,10 @@ def _train_worker(rank, world):
     ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(1 + rank)).to(dev)
     losses = {}
     for backend in ("torch", "symm"):
-        model = build_llama(cfg, dev, comm_backend=backend, fused_gather=True)
+        # with the multicast transports the reduce-scatter under test is the switch's (multimem.ld_reduce), so the gradients
+        # are not pushed from the GEMM epilogues instead; otherwise the default of this world size runs
+        fused_reduce = False if os.environ.get("YAFSDP_SYMM_TRANSPORT") == "mc" else None
+        model = build_llama(cfg, dev, comm_backend=backend, fused_gather=True, fused_reduce=fused_reduce)
         opt = ShardedAdamW(model, lr=1e-3, max_grad_norm=1.0)
         step = TrainStep(model, opt, dev)
         losses[backend] = [step(ids).item() for _ in range(4)]

@@ -35,10 +35,10 @@ def _entry(rank, world, port, fn, errq, transport=None):
         torch.cuda.synchronize()
     except Exception:
         errq.put((rank, traceback.format_exc()))
-        raise
-    finally:
-        if dist.is_initialized():
-            dist.destroy_process_group()
+        # leave at once, between steps as far as this rank is concerned: tearing the process group down here could wait for
+        # collectives that the peers will never join
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 def _run(fn, world, transport=None):

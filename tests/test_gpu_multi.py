@@ -35,8 +35,12 @@ def _entry(rank, world, port, fn, errq, transport=None):
         torch.cuda.synchronize()
     except Exception:
         errq.put((rank, traceback.format_exc()))
-        # leave at once, between steps as far as this rank is concerned: tearing the process group down here could wait for
-        # collectives that the peers will never join
+        # leave with nothing of this rank in flight (every device-side wait is bounded), but without tearing the process
+        # group down: that could wait for collectives that the peers will never join
+        try:
+            torch.cuda.synchronize()
+        except Exception:
+            pass
         os._exit(1)
     dist.destroy_process_group()
 

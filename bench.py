@@ -259,12 +259,21 @@ def make_step_ours(args, rank: int, world: int, device: torch.device):
 
     backend = args.comm_backend if args.comm_backend != "auto" else ("symm" if world > 1 else "none (single rank: buffers aliased)")
 
+    pushed_groups: list = []
+
     def dry_run(on: bool) -> None:
         be = model._get_fsdp_state()._comm_ctx.backend
         if hasattr(be, "dry_run"):
             torch.cuda.synchronize()
             dist.barrier()
             be.dry_run = on
+            # gradients pushed from the GEMM epilogues would still cross NVLink: the compute-only step reduces locally
+            from yafsdp_b200.optim import param_groups_of
+
+            if on:
+                pushed_groups[:] = [g for g in param_groups_of(model) if g.fused_reduce]
+            for g in pushed_groups:
+                g.fused_reduce = not on
 
     detail = {"comm_backend": backend, "params": cfg.num_params(), "_finish": opt.join, "reshard_after_forward": reshard}
     if backend == "symm":

@@ -1,5 +1,5 @@
 """Hugging Face integration on CPU/gloo (world 2): a tiny ``LlamaForCausalLM`` sharded through ``shard_causal_lm`` (both APIs,
-tied and untied embeddings, activation checkpointing, weights only on rank 0) trains like the unsharded model."""
+tied and untied embeddings, activation checkpointing, weights only on rank 0) trains like the unsharded model; so do GPT-2, GPT-NeoX, Mistral, Qwen2, Mixtral (mixture of experts) and Gemma."""
 
 import pytest
 import torch
@@ -77,6 +77,25 @@ def _tiny_other(kind):
 
         return GPT2LMHeadModel(GPT2Config(n_embd=32, n_layer=2, n_head=4, vocab_size=64, n_positions=32, resid_pdrop=0.0,
                                           embd_pdrop=0.0, attn_pdrop=0.0, attn_implementation="eager"))
+    common = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=64,
+                  max_position_embeddings=64, attention_dropout=0.0, attn_implementation="eager")
+    if kind == "mistral":  # sliding-window attention configuration, grouped KV heads
+        from transformers import MistralConfig, MistralForCausalLM
+
+        return MistralForCausalLM(MistralConfig(sliding_window=8, **common))
+    if kind == "qwen2":  # biases on the q/k/v projections: 1-D parameters inside every layer group
+        from transformers import Qwen2Config, Qwen2ForCausalLM
+
+        return Qwen2ForCausalLM(Qwen2Config(**common))
+    if kind == "mixtral":  # mixture of experts: router + expert weights in every layer, all flat-sharded over the data ranks
+        from transformers import MixtralConfig, MixtralForCausalLM
+
+        return MixtralForCausalLM(MixtralConfig(num_local_experts=4, num_experts_per_tok=2, router_aux_loss_coef=0.0,
+                                                output_router_logits=False, **common))
+    if kind == "gemma":  # tied embeddings, (1 + weight) RMSNorm, explicit head_dim
+        from transformers import GemmaConfig, GemmaForCausalLM
+
+        return GemmaForCausalLM(GemmaConfig(head_dim=8, **common))
     from transformers import GPTNeoXConfig, GPTNeoXForCausalLM  # parallel residual, `gpt_neox.layers`, `embed_out`
 
     return GPTNeoXForCausalLM(GPTNeoXConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
@@ -106,7 +125,7 @@ def _other_worker(rank, world, kind):
 
 
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("kind", ["gpt2", "neox"])
+@pytest.mark.parametrize("kind", ["gpt2", "neox", "mistral", "qwen2", "mixtral", "gemma"])
 def test_hf_other_decoder_layouts(kind):
     run_distributed(_other_worker, 2, kind)
 
